@@ -1,0 +1,175 @@
+/*
+ * C ABI of the B200 image-transform-and-batch library (libmlxd_b200.so).
+ *
+ * mlx-data has no C ABI of its own: its boundary for this path is a set of C++
+ * virtuals (op::ImageTransformOp::apply_image, stream::Batch::next,
+ * core::merge_batch).  The entry points below are what those virtuals bind to
+ * when the path runs on the GPU; each one names the reference interface it
+ * replaces.  Plain pointers and sizes only, an int status on every call, no
+ * exceptions and no C++ or torch types cross this boundary.
+ *
+ * Images are [H, W, C] uint8, C-contiguous (mlx/data/core/image/Image.h:35-49),
+ * 1 <= C <= 4.  A batch is [N, slot_h, slot_w, C_out], C-contiguous.
+ */
+#ifndef MLXD_B200_H
+#define MLXD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MLXD_API __attribute__((visibility("default")))
+
+typedef struct mlxd_ctx mlxd_ctx;
+
+enum mlxd_status {
+  MLXD_OK = 0,
+  MLXD_ERR_INVALID = 1,     /* bad argument; mlxd_last_error() says which */
+  MLXD_ERR_CUDA = 2,        /* a CUDA call failed; message carries its text */
+  MLXD_ERR_NOMEM = 3,       /* host or device allocation failed */
+  MLXD_ERR_TIMEOUT = 4,     /* mlxd_batch_wait ran out of time; work still queued */
+  MLXD_ERR_UNSUPPORTED = 5, /* a shape this build cannot run on the device */
+  MLXD_ERR_DEVICE = 6       /* the kernel recorded a failed self-check */
+};
+
+enum mlxd_geom {
+  MLXD_GEOM_NONE = 0,
+  MLXD_GEOM_RESIZE = 1, /* core::image::resize, mlx/data/core/image/ImageTransform.cpp:41-62 */
+  MLXD_GEOM_AFFINE = 2  /* core::image::affine, mlx/data/core/image/ImageTransform.cpp:75-111 */
+};
+
+enum mlxd_dtype { MLXD_U8 = 0, MLXD_F32 = 1 };
+enum mlxd_mem { MLXD_MEM_HOST = 0, MLXD_MEM_DEVICE = 1 };
+
+/*
+ * One sample's op chain, already reduced by the caller to the canonical order
+ *   source -> window+mirror -> one geometric op -> window+mirror -> [gray] -> slot.
+ * It stands for a run of op::ImageTransformOp::apply_image calls
+ * (mlx/data/op/ImageTransform.cpp:78-369) on one key of one sample:
+ *   pre_*   crops (core::image::crop, ImageTransform.cpp:64-73) and horizontal
+ *           flips (core::image::hflip, :123-140) that come before the geometric op;
+ *   geom    image_resize / image_resize_smallest_side (target size in geom_w,
+ *           geom_h) or image_rotate (matrix in mx, output size in geom_w, geom_h,
+ *           both computed by the caller exactly as :80-86 and :113-121 do);
+ *   post_*  crops and flips after it.
+ * With geom == NONE the geometric output is the pre window itself and
+ * geom_w, geom_h must equal pre_w, pre_h.  Random parameters (crop rectangles,
+ * flip decisions) are drawn by the caller on the host.
+ */
+typedef struct mlxd_sample_desc {
+  const uint8_t* src; /* [src_h, src_w, C] */
+  int32_t src_h, src_w;
+  int32_t pre_x, pre_y, pre_w, pre_h;
+  int32_t pre_flip;
+  int32_t geom;
+  int32_t geom_w, geom_h;
+  float mx[6];
+  int32_t post_x, post_y, post_w, post_h;
+  int32_t post_flip;
+  int32_t reserved;
+} mlxd_sample_desc;
+
+/*
+ * The batch the samples are written into: array::batch
+ * (mlx/data/Array.cpp:465-498) with core::BatchShape (mlx/data/core/BatchShape.cpp:26-45)
+ * followed by the cast that reference pipelines run as a Python lambda
+ * (README.md:55-57): x.astype(float32) / 255, optionally (x/255 - mean) / std.
+ * Sample i occupies slot i; its post window sits in the slot's top-left corner
+ * and the rest of the slot holds the pad value (cast like every other pixel).
+ */
+typedef struct mlxd_batch_desc {
+  void* dst;           /* [n, slot_h, slot_w, C_out] of out_dtype */
+  int32_t slot_h, slot_w;
+  int32_t channels;    /* C of every source image */
+  int32_t gray;        /* 1: core::image::channel_reduction (ImageTransform.cpp:142-182) after the post window; C_out = 1 */
+  int32_t gray_m[3];   /* its 16.16 fixed-point multipliers, (int)(coef * 65536) */
+  int32_t gray_bias;   /* (int)(bias * 65536) */
+  int32_t out_dtype;   /* MLXD_U8: raw bytes; MLXD_F32: cast below */
+  int32_t normalise;   /* 0: x / divisor; 1: (x / divisor - mean[c]) / std[c] */
+  float divisor;       /* 255 for the usual cast; 1 gives a plain astype */
+  float mean[4];
+  float std_[4];
+  double pad_value;    /* batch pad value, converted to uint8 like Array::fill (mlx/data/Array.cpp:123-134) */
+  int32_t src_mem;     /* mlxd_mem of every sample's src */
+  int32_t dst_mem;     /* mlxd_mem of dst */
+} mlxd_batch_desc;
+
+typedef struct mlxd_stats {
+  uint64_t batches;        /* fused launches issued */
+  uint64_t samples;
+  uint64_t kernel_launches;
+  uint64_t h2d_bytes;
+  uint64_t d2h_bytes;
+  uint64_t device_bytes_reserved; /* staging + output arenas currently held */
+} mlxd_stats;
+
+/* Context: one device, n_lanes independent lanes.  A lane owns a CUDA stream, a
+ * device staging arena and an output arena; calls on one lane are stream
+ * ordered, different lanes overlap.  Replaces the role of core::ThreadPool
+ * workers under stream::Prefetch (mlx/data/stream/Prefetch.cpp:29-56): one
+ * prefetch worker drives one lane. */
+MLXD_API int mlxd_ctx_create(int device, int n_lanes, mlxd_ctx** out);
+MLXD_API void mlxd_ctx_destroy(mlxd_ctx* ctx);
+
+/* Text of the last error raised on the calling thread. */
+MLXD_API const char* mlxd_last_error(void);
+
+/* Page-locked host memory for sample and batch storage; backs Array storage
+ * through the external-storage constructor (mlx/data/Array.h:28-31). */
+MLXD_API void* mlxd_pinned_alloc(size_t bytes);
+MLXD_API void mlxd_pinned_free(void* p);
+
+/* Enqueue one fused batch on a lane and return: host sources are copied to the
+ * device (only the rows the chain reads), one kernel writes every slot, and a
+ * host dst is copied back.  Replaces stream::Batch::next -> core::merge_batch
+ * (mlx/data/stream/Batch.cpp:25-39, mlx/data/core/Utils.cpp:209-252) together
+ * with the per-sample op calls listed at mlxd_sample_desc.  Host memory must
+ * stay untouched until mlxd_batch_wait returns MLXD_OK. */
+MLXD_API int mlxd_fused_batch(
+    mlxd_ctx* ctx, int lane, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch);
+
+/* Wait for everything queued on a lane, at most timeout_ms (< 0: no limit).
+ * Replaces future.get() in stream::Prefetch::next (mlx/data/stream/Prefetch.cpp:43-53). */
+MLXD_API int mlxd_batch_wait(mlxd_ctx* ctx, int lane, int timeout_ms);
+
+/* Same work for device-resident sources and destination, launched on the
+ * caller's CUDA stream (a cudaStream_t passed as void*; NULL is the default
+ * stream).  Nothing is copied except the descriptors. */
+MLXD_API int mlxd_fused_batch_on_stream(
+    mlxd_ctx* ctx, void* cuda_stream, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch);
+
+/* One entry per named op, host buffers in and out, synchronous; for chains
+ * that cannot be fused (a host callback between two ops).  Each runs the same
+ * kernel with a one-stage program. */
+/* core::image::resize, mlx/data/core/image/ImageTransform.cpp:41-62 */
+MLXD_API int mlxd_image_resize(
+    mlxd_ctx* ctx, const uint8_t* src, int h, int w, int c, uint8_t* dst, int dh, int dw);
+/* core::image::crop, mlx/data/core/image/ImageTransform.cpp:64-73 */
+MLXD_API int mlxd_image_crop(
+    mlxd_ctx* ctx, const uint8_t* src, int h, int w, int c, int x, int y, int cw, int ch, uint8_t* dst);
+/* core::image::hflip, mlx/data/core/image/ImageTransform.cpp:123-140 */
+MLXD_API int mlxd_image_hflip(mlxd_ctx* ctx, const uint8_t* src, int h, int w, int c, uint8_t* dst);
+/* core::image::affine, mlx/data/core/image/ImageTransform.cpp:75-111; th, tw as computed at :80-86 */
+MLXD_API int mlxd_image_affine(
+    mlxd_ctx* ctx, const uint8_t* src, int h, int w, int c, const float mx[6], int th, int tw, uint8_t* dst);
+/* core::image::channel_reduction, mlx/data/core/image/ImageTransform.cpp:142-182 */
+MLXD_API int mlxd_image_channel_reduction(
+    mlxd_ctx* ctx, const uint8_t* src, int h, int w, const int32_t m_fixed[3], int32_t bias_fixed, uint8_t* dst);
+/* array::batch for uint8 images, mlx/data/Array.cpp:465-498 */
+MLXD_API int mlxd_batch_pad(
+    mlxd_ctx* ctx, const uint8_t* const* srcs, const int32_t* hs, const int32_t* ws, int n, int c,
+    int slot_h, int slot_w, double pad_value, uint8_t* dst);
+/* the float32 cast of README.md:55-57; count pixels of c channels */
+MLXD_API int mlxd_cast_scale_normalise(
+    mlxd_ctx* ctx, const uint8_t* src, int64_t count, int c, float divisor,
+    const float* mean, const float* std_, float* dst);
+
+MLXD_API int mlxd_stats_get(mlxd_ctx* ctx, mlxd_stats* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLXD_B200_H */

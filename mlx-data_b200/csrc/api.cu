@@ -1,0 +1,396 @@
+// extern "C" entry points declared in include/mlxd_b200.h.
+#include <cstring>
+#include <new>
+
+#include "context.h"
+
+using namespace mlxd;
+
+namespace {
+
+thread_local std::string g_last;
+
+void destroy_lane(Lane* l) {
+  if (!l) {
+    return;
+  }
+  if (l->stream) {
+    cudaStreamSynchronize(l->stream);
+  }
+  for (int s = 0; s < kDescSlots; s++) {
+    if (l->d_desc[s].ptr) cudaFree(l->d_desc[s].ptr);
+    if (l->h_desc[s].ptr) cudaFreeHost(l->h_desc[s].ptr);
+    if (l->desc_copied[s]) cudaEventDestroy(l->desc_copied[s]);
+  }
+  if (l->d_src.ptr) cudaFree(l->d_src.ptr);
+  if (l->d_out.ptr) cudaFree(l->d_out.ptr);
+  if (l->h_status) cudaFreeHost(l->h_status);
+  if (l->done) cudaEventDestroy(l->done);
+  if (l->stream) cudaStreamDestroy(l->stream);
+  delete l;
+}
+
+int make_lane(Lane** out) {
+  Lane* l = new (std::nothrow) Lane();
+  if (!l) {
+    return fail(MLXD_ERR_NOMEM, "out of host memory");
+  }
+  cudaError_t e = cudaStreamCreateWithFlags(&l->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&l->done, cudaEventDisableTiming);
+  for (int s = 0; s < kDescSlots && e == cudaSuccess; s++) {
+    e = cudaEventCreateWithFlags(&l->desc_copied[s], cudaEventDisableTiming);
+  }
+  if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&l->h_status), sizeof(int32_t), cudaHostAllocDefault);
+  if (e != cudaSuccess) {
+    destroy_lane(l);
+    return fail_cuda(e, "lane setup");
+  }
+  *l->h_status = 0;
+  *out = l;
+  return MLXD_OK;
+}
+
+// Synchronous run of one launch on the context's private lane.
+int run_sync(mlxd_ctx* ctx, const mlxd_sample_desc* s, int n, const mlxd_batch_desc* b) {
+  Lane& lane = *ctx->lanes[ctx->n_user_lanes];
+  int rc = enqueue_on_lane(ctx, lane, s, n, b, nullptr);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
+  return wait_lane(ctx, lane, -1);
+}
+
+mlxd_sample_desc whole_image(const uint8_t* src, int h, int w) {
+  mlxd_sample_desc d;
+  std::memset(&d, 0, sizeof(d));
+  d.src = src;
+  d.src_h = h;
+  d.src_w = w;
+  d.pre_w = w;
+  d.pre_h = h;
+  d.geom = MLXD_GEOM_NONE;
+  d.geom_w = w;
+  d.geom_h = h;
+  d.post_w = w;
+  d.post_h = h;
+  return d;
+}
+
+mlxd_batch_desc u8_batch(void* dst, int slot_h, int slot_w, int c) {
+  mlxd_batch_desc b;
+  std::memset(&b, 0, sizeof(b));
+  b.dst = dst;
+  b.slot_h = slot_h;
+  b.slot_w = slot_w;
+  b.channels = c;
+  b.out_dtype = MLXD_U8;
+  b.divisor = 1.0f;
+  b.src_mem = MLXD_MEM_HOST;
+  b.dst_mem = MLXD_MEM_HOST;
+  return b;
+}
+
+} // namespace
+
+extern "C" {
+
+int mlxd_ctx_create(int device, int n_lanes, mlxd_ctx** out) {
+  if (!out || n_lanes < 1 || n_lanes > 256) {
+    return fail(MLXD_ERR_INVALID, "mlxd_ctx_create: need an output pointer and 1..256 lanes");
+  }
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "cudaGetDeviceCount");
+  }
+  if (device < 0 || device >= count) {
+    return fail(MLXD_ERR_INVALID, "mlxd_ctx_create: no such CUDA device");
+  }
+  MLXD_CUDA(cudaSetDevice(device));
+  mlxd_ctx* ctx = new (std::nothrow) mlxd_ctx();
+  if (!ctx) {
+    return fail(MLXD_ERR_NOMEM, "out of host memory");
+  }
+  ctx->device = device;
+  ctx->n_user_lanes = n_lanes;
+  e = cudaMalloc(reinterpret_cast<void**>(&ctx->d_status), sizeof(int32_t));
+  if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int32_t));
+  if (e != cudaSuccess) {
+    mlxd_ctx_destroy(ctx);
+    return fail_cuda(e, "status word");
+  }
+  // user lanes, then one private lane for the synchronous ops and one whose
+  // descriptor ring serves launches on caller streams
+  for (int i = 0; i < n_lanes + 2; i++) {
+    Lane* l = nullptr;
+    int rc = make_lane(&l);
+    if (rc != MLXD_OK) {
+      mlxd_ctx_destroy(ctx);
+      return rc;
+    }
+    ctx->lanes.push_back(l);
+  }
+  *out = ctx;
+  return MLXD_OK;
+}
+
+void mlxd_ctx_destroy(mlxd_ctx* ctx) {
+  if (!ctx) {
+    return;
+  }
+  cudaSetDevice(ctx->device);
+  for (Lane* l : ctx->lanes) {
+    destroy_lane(l);
+  }
+  for (auto& kv : ctx->luts) {
+    cudaFree(kv.second);
+  }
+  if (ctx->d_status) {
+    cudaFree(ctx->d_status);
+  }
+  delete ctx;
+}
+
+const char* mlxd_last_error(void) {
+  g_last = error_text();
+  return g_last.c_str();
+}
+
+void* mlxd_pinned_alloc(size_t bytes) {
+  void* p = nullptr;
+  if (bytes == 0) {
+    bytes = 1;
+  }
+  cudaError_t e = cudaHostAlloc(&p, bytes, cudaHostAllocPortable);
+  if (e != cudaSuccess) {
+    fail_cuda(e, "cudaHostAlloc");
+    return nullptr;
+  }
+  return p;
+}
+
+void mlxd_pinned_free(void* p) {
+  if (p) {
+    cudaFreeHost(p);
+  }
+}
+
+int mlxd_fused_batch(
+    mlxd_ctx* ctx, int lane, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch) {
+  if (!ctx || lane < 0 || lane >= ctx->n_user_lanes) {
+    return fail(MLXD_ERR_INVALID, "mlxd_fused_batch: bad context or lane index");
+  }
+  return enqueue_on_lane(ctx, *ctx->lanes[lane], samples, n, batch, nullptr);
+}
+
+int mlxd_batch_wait(mlxd_ctx* ctx, int lane, int timeout_ms) {
+  if (!ctx || lane < 0 || lane >= ctx->n_user_lanes) {
+    return fail(MLXD_ERR_INVALID, "mlxd_batch_wait: bad context or lane index");
+  }
+  return wait_lane(ctx, *ctx->lanes[lane], timeout_ms);
+}
+
+int mlxd_fused_batch_on_stream(
+    mlxd_ctx* ctx, void* cuda_stream, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch) {
+  if (!ctx || !samples || !batch || n < 0) {
+    return fail(MLXD_ERR_INVALID, "mlxd_fused_batch_on_stream: null argument");
+  }
+  if (n == 0) {
+    return MLXD_OK;
+  }
+  if (batch->src_mem != MLXD_MEM_DEVICE || batch->dst_mem != MLXD_MEM_DEVICE || !batch->dst) {
+    return fail(MLXD_ERR_INVALID, "mlxd_fused_batch_on_stream: sources and destination must be device memory");
+  }
+  MLXD_CUDA(cudaSetDevice(ctx->device));
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // validate + plan
+  std::vector<DevSample> dev;
+  bool any_resize = false;
+  mlxd_batch_desc b = *batch;
+  Lane& ring = *ctx->lanes[ctx->n_user_lanes + 1];
+  LaunchParams p;
+  int rc = prepare_launch(ctx, &b, n, p);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
+  rc = plan_samples(samples, n, &b, dev, any_resize);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
+  const size_t esize = p.out_f32 ? 4 : 1;
+  const size_t slot_bytes = (size_t)b.slot_h * b.slot_w * p.c_out * esize;
+  for (int i = 0; i < n; i++) {
+    dev[i].dst = static_cast<uint8_t*>(b.dst) + slot_bytes * i;
+  }
+  std::lock_guard<std::mutex> guard(ring.mu);
+  const int slot = ring.next_slot;
+  ring.next_slot = (slot + 1) % kDescSlots;
+  // Here the slot's event is recorded after the kernel, so a finished wait
+  // means neither the copy nor the kernel still needs the tables.
+  MLXD_CUDA(cudaEventSynchronize(ring.desc_copied[slot]));
+  rc = arena_reserve(ctx, ring.h_desc[slot], sizeof(DevSample) * n, true, nullptr);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
+  rc = arena_reserve(ctx, ring.d_desc[slot], sizeof(DevSample) * n, false, nullptr);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
+  std::memcpy(ring.h_desc[slot].ptr, dev.data(), sizeof(DevSample) * n);
+  MLXD_CUDA(cudaMemcpyAsync(
+      ring.d_desc[slot].ptr, ring.h_desc[slot].ptr, sizeof(DevSample) * n, cudaMemcpyHostToDevice, stream));
+  p.samples = static_cast<const DevSample*>(ring.d_desc[slot].ptr);
+  MLXD_CUDA(launch_fused_batch(p, any_resize, stream));
+  MLXD_CUDA(cudaEventRecord(ring.desc_copied[slot], stream));
+  ctx->batches += 1;
+  ctx->samples += n;
+  ctx->launches += 1;
+  return MLXD_OK;
+}
+
+int mlxd_image_resize(mlxd_ctx* ctx, const uint8_t* src, int h, int w, int c, uint8_t* dst, int dh, int dw) {
+  if (!ctx || !src || !dst) {
+    return fail(MLXD_ERR_INVALID, "mlxd_image_resize: null argument");
+  }
+  if (dh <= 0 || dw <= 0) {
+    return fail(MLXD_ERR_INVALID, "image: cannot create image with 0 or negative dimension");
+  }
+  mlxd_sample_desc d = whole_image(src, h, w);
+  d.geom = MLXD_GEOM_RESIZE;
+  d.geom_w = dw;
+  d.geom_h = dh;
+  d.post_w = dw;
+  d.post_h = dh;
+  mlxd_batch_desc b = u8_batch(dst, dh, dw, c);
+  return run_sync(ctx, &d, 1, &b);
+}
+
+int mlxd_image_crop(
+    mlxd_ctx* ctx, const uint8_t* src, int h, int w, int c, int x, int y, int cw, int ch, uint8_t* dst) {
+  if (!ctx || !src || !dst) {
+    return fail(MLXD_ERR_INVALID, "mlxd_image_crop: null argument");
+  }
+  mlxd_sample_desc d = whole_image(src, h, w);
+  d.post_x = x;
+  d.post_y = y;
+  d.post_w = cw;
+  d.post_h = ch;
+  mlxd_batch_desc b = u8_batch(dst, ch, cw, c);
+  return run_sync(ctx, &d, 1, &b);
+}
+
+int mlxd_image_hflip(mlxd_ctx* ctx, const uint8_t* src, int h, int w, int c, uint8_t* dst) {
+  if (!ctx || !src || !dst) {
+    return fail(MLXD_ERR_INVALID, "mlxd_image_hflip: null argument");
+  }
+  mlxd_sample_desc d = whole_image(src, h, w);
+  d.post_flip = 1;
+  mlxd_batch_desc b = u8_batch(dst, h, w, c);
+  return run_sync(ctx, &d, 1, &b);
+}
+
+int mlxd_image_affine(
+    mlxd_ctx* ctx, const uint8_t* src, int h, int w, int c, const float mx[6], int th, int tw, uint8_t* dst) {
+  if (!ctx || !src || !dst || !mx) {
+    return fail(MLXD_ERR_INVALID, "mlxd_image_affine: null argument");
+  }
+  if (th <= 0 || tw <= 0) {
+    return fail(MLXD_ERR_INVALID, "image: cannot create image with 0 or negative dimension");
+  }
+  mlxd_sample_desc d = whole_image(src, h, w);
+  d.geom = MLXD_GEOM_AFFINE;
+  d.geom_w = tw;
+  d.geom_h = th;
+  d.post_w = tw;
+  d.post_h = th;
+  std::memcpy(d.mx, mx, sizeof(d.mx));
+  mlxd_batch_desc b = u8_batch(dst, th, tw, c);
+  return run_sync(ctx, &d, 1, &b);
+}
+
+int mlxd_image_channel_reduction(
+    mlxd_ctx* ctx, const uint8_t* src, int h, int w, const int32_t m_fixed[3], int32_t bias_fixed, uint8_t* dst) {
+  if (!ctx || !src || !dst || !m_fixed) {
+    return fail(MLXD_ERR_INVALID, "mlxd_image_channel_reduction: null argument");
+  }
+  mlxd_sample_desc d = whole_image(src, h, w);
+  mlxd_batch_desc b = u8_batch(dst, h, w, 3);
+  b.gray = 1;
+  b.gray_m[0] = m_fixed[0];
+  b.gray_m[1] = m_fixed[1];
+  b.gray_m[2] = m_fixed[2];
+  b.gray_bias = bias_fixed;
+  return run_sync(ctx, &d, 1, &b);
+}
+
+int mlxd_batch_pad(
+    mlxd_ctx* ctx, const uint8_t* const* srcs, const int32_t* hs, const int32_t* ws, int n, int c,
+    int slot_h, int slot_w, double pad_value, uint8_t* dst) {
+  if (!ctx || !srcs || !hs || !ws || !dst || n < 0) {
+    return fail(MLXD_ERR_INVALID, "mlxd_batch_pad: null argument");
+  }
+  std::vector<mlxd_sample_desc> d((size_t)n);
+  for (int i = 0; i < n; i++) {
+    d[i] = whole_image(srcs[i], hs[i], ws[i]);
+  }
+  mlxd_batch_desc b = u8_batch(dst, slot_h, slot_w, c);
+  b.pad_value = pad_value;
+  return run_sync(ctx, d.data(), n, &b);
+}
+
+int mlxd_cast_scale_normalise(
+    mlxd_ctx* ctx, const uint8_t* src, int64_t count, int c, float divisor,
+    const float* mean, const float* std_, float* dst) {
+  if (!ctx || !src || !dst || count < 0 || c < 1 || c > 4) {
+    return fail(MLXD_ERR_INVALID, "mlxd_cast_scale_normalise: bad argument");
+  }
+  if ((mean == nullptr) != (std_ == nullptr)) {
+    return fail(MLXD_ERR_INVALID, "mlxd_cast_scale_normalise: mean and std come together");
+  }
+  // The pixel run is cast as a [rows, 4096] image followed by one short row.
+  const int64_t kRow = 4096;
+  const int64_t rows = count / kRow;
+  const int64_t rem = count - rows * kRow;
+  if (rows > 0x7fffffff) {
+    return fail(MLXD_ERR_INVALID, "mlxd_cast_scale_normalise: too many pixels");
+  }
+  for (int part = 0; part < 2; part++) {
+    const int h = part == 0 ? (int)rows : 1;
+    const int w = part == 0 ? (int)kRow : (int)rem;
+    if (h == 0 || w == 0) {
+      continue;
+    }
+    const int64_t off = part == 0 ? 0 : rows * kRow * c;
+    mlxd_sample_desc d = whole_image(src + off, h, w);
+    mlxd_batch_desc b = u8_batch(dst + off, h, w, c);
+    b.out_dtype = MLXD_F32;
+    b.divisor = divisor;
+    if (mean) {
+      b.normalise = 1;
+      for (int k = 0; k < c; k++) {
+        b.mean[k] = mean[k];
+        b.std_[k] = std_[k];
+      }
+    }
+    int rc = run_sync(ctx, &d, 1, &b);
+    if (rc != MLXD_OK) {
+      return rc;
+    }
+  }
+  return MLXD_OK;
+}
+
+int mlxd_stats_get(mlxd_ctx* ctx, mlxd_stats* out) {
+  if (!ctx || !out) {
+    return fail(MLXD_ERR_INVALID, "mlxd_stats_get: null argument");
+  }
+  out->batches = ctx->batches.load();
+  out->samples = ctx->samples.load();
+  out->kernel_launches = ctx->launches.load();
+  out->h2d_bytes = ctx->h2d.load();
+  out->d2h_bytes = ctx->d2h.load();
+  out->device_bytes_reserved = ctx->reserved.load();
+  return MLXD_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,439 @@
+// Context, lanes, descriptor planning and the enqueue path of the C ABI.
+#include "context.h"
+
+#include <chrono>
+#include <cmath>
+#include <cstring>
+#include <thread>
+
+namespace mlxd {
+
+namespace {
+thread_local std::string g_error;
+}
+
+const std::string& error_text() {
+  return g_error;
+}
+
+void set_error(const std::string& msg) {
+  g_error = msg;
+}
+
+int fail(int code, const std::string& msg) {
+  g_error = msg;
+  return code;
+}
+
+int fail_cuda(cudaError_t e, const char* what) {
+  g_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return e == cudaErrorMemoryAllocation ? MLXD_ERR_NOMEM : MLXD_ERR_CUDA;
+}
+
+bool LutKey::operator<(const LutKey& o) const {
+  return std::memcmp(this, &o, sizeof(LutKey)) < 0;
+}
+
+int arena_reserve(mlxd_ctx* ctx, Arena& a, size_t bytes, bool pinned, cudaStream_t stream_to_drain) {
+  if (bytes <= a.cap) {
+    return MLXD_OK;
+  }
+  // Work already queued may still read the old block.
+  if (stream_to_drain) {
+    MLXD_CUDA(cudaStreamSynchronize(stream_to_drain));
+  }
+  size_t want = bytes + bytes / 4;
+  want = (want + 4095) & ~(size_t)4095;
+  void* p = nullptr;
+  if (pinned) {
+    MLXD_CUDA(cudaHostAlloc(&p, want, cudaHostAllocDefault));
+    if (a.ptr) {
+      cudaFreeHost(a.ptr);
+    }
+  } else {
+    if (a.ptr) {
+      cudaFree(a.ptr);
+      ctx->reserved -= a.cap;
+      a.ptr = nullptr;
+      a.cap = 0;
+    }
+    MLXD_CUDA(cudaMalloc(&p, want));
+    ctx->reserved += want;
+  }
+  a.ptr = p;
+  a.cap = want;
+  return MLXD_OK;
+}
+
+static int check_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, int slot_h, int slot_w) {
+  const std::string at = "sample " + std::to_string(i) + ": ";
+  if (!d.src) {
+    return fail(MLXD_ERR_INVALID, at + "null source");
+  }
+  if (d.src_h <= 0 || d.src_w <= 0) {
+    return fail(MLXD_ERR_INVALID, at + "image: cannot create image with 0 or negative dimension");
+  }
+  if (d.pre_w <= 0 || d.pre_h <= 0 || d.pre_x < 0 || d.pre_y < 0 ||
+      (int64_t)d.pre_x + d.pre_w > d.src_w || (int64_t)d.pre_y + d.pre_h > d.src_h) {
+    return fail(MLXD_ERR_INVALID, at + "window before the geometric op leaves the source image");
+  }
+  if (d.geom < MLXD_GEOM_NONE || d.geom > MLXD_GEOM_AFFINE) {
+    return fail(MLXD_ERR_INVALID, at + "unknown geometric op");
+  }
+  if (d.geom_w <= 0 || d.geom_h <= 0) {
+    return fail(MLXD_ERR_INVALID, at + "image: cannot create image with 0 or negative dimension");
+  }
+  if (d.geom == MLXD_GEOM_NONE && (d.geom_w != d.pre_w || d.geom_h != d.pre_h)) {
+    return fail(MLXD_ERR_INVALID, at + "geom_w, geom_h must equal pre_w, pre_h without a geometric op");
+  }
+  if (d.post_w <= 0 || d.post_h <= 0 || d.post_x < 0 || d.post_y < 0 ||
+      (int64_t)d.post_x + d.post_w > d.geom_w || (int64_t)d.post_y + d.post_h > d.geom_h) {
+    return fail(MLXD_ERR_INVALID, at + "window after the geometric op leaves its output");
+  }
+  if (d.post_w > slot_w || d.post_h > slot_h) {
+    return fail(MLXD_ERR_INVALID, at + "result is larger than its slot in the batch");
+  }
+  if ((int64_t)d.src_h * d.src_w * b->channels >= ((int64_t)1 << 40)) {
+    return fail(MLXD_ERR_INVALID, at + "source image too large");
+  }
+  return MLXD_OK;
+}
+
+static int plan_resize(DevSample& s, int C, int i) {
+  int sub_h = kTileH, sub_w = kTileW;
+  for (;;) {
+    AxisPlan ay = plan_axis(s.pre_h, s.geom_h, sub_h);
+    AxisPlan ax = plan_axis(s.pre_w, s.geom_w, sub_w);
+    const int64_t ext_y = std::min<int64_t>(ay.extent, s.pre_h);
+    const int64_t ext_x = std::min<int64_t>(ax.extent, s.pre_w);
+    const int64_t pitch = (ext_x * C + 3) & ~(int64_t)3;
+    const bool ok = ext_y * pitch <= kSrcTileBytes && (int64_t)sub_h * pitch <= kMidFloats &&
+        (int64_t)sub_h * ay.cap + (int64_t)sub_w * ax.cap <= kWeightFloats;
+    if (ok) {
+      s.sub_h = sub_h;
+      s.sub_w = sub_w;
+      s.cap_y = ay.cap;
+      s.cap_x = ax.cap;
+      return MLXD_OK;
+    }
+    if (sub_h > 4) {
+      sub_h /= 2;
+    } else if (sub_w > 8) {
+      sub_w /= 2;
+    } else if (sub_h > 1) {
+      sub_h /= 2;
+    } else if (sub_w > 1) {
+      sub_w /= 2;
+    } else {
+      return fail(
+          MLXD_ERR_UNSUPPORTED,
+          "sample " + std::to_string(i) + ": shrink ratio too large for the on-chip filter footprint");
+    }
+  }
+}
+
+int plan_samples(
+    const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b,
+    std::vector<DevSample>& out, bool& any_resize) {
+  any_resize = false;
+  out.resize(n);
+  for (int i = 0; i < n; i++) {
+    const mlxd_sample_desc& d = samples[i];
+    int rc = check_sample(d, i, b, b->slot_h, b->slot_w);
+    if (rc != MLXD_OK) {
+      return rc;
+    }
+    DevSample s;
+    std::memset(&s, 0, sizeof(s));
+    s.src = d.src;
+    s.src_h = d.src_h;
+    s.src_w = d.src_w;
+    s.pre_x = d.pre_x;
+    s.pre_y = d.pre_y;
+    s.pre_w = d.pre_w;
+    s.pre_h = d.pre_h;
+    s.pre_flip = d.pre_flip ? 1 : 0;
+    s.geom_w = d.geom_w;
+    s.geom_h = d.geom_h;
+    s.post_x = d.post_x;
+    s.post_y = d.post_y;
+    s.post_w = d.post_w;
+    s.post_h = d.post_h;
+    s.post_flip = d.post_flip ? 1 : 0;
+    s.slot_h = b->slot_h;
+    s.slot_w = b->slot_w;
+    std::memcpy(s.mx, d.mx, sizeof(s.mx));
+    s.sub_h = kTileH;
+    s.sub_w = kTileW;
+    s.cap_y = s.cap_x = 1;
+    if (d.geom == MLXD_GEOM_RESIZE) {
+      if (d.pre_w == d.geom_w && d.pre_h == d.geom_h) {
+        s.mode = kModeCopy;  // identity on both axes
+      } else {
+        s.mode = kModeResize;
+        rc = plan_resize(s, b->channels, i);
+        if (rc != MLXD_OK) {
+          return rc;
+        }
+        any_resize = true;
+      }
+    } else if (d.geom == MLXD_GEOM_AFFINE) {
+      s.mode = kModeAffine;
+    } else {
+      s.mode = kModeCopy;
+    }
+    if (s.mode == kModeCopy && s.pre_flip) {
+      // Without a geometric op the two mirrors compose into one.
+      s.pre_flip = 0;
+      s.post_flip ^= 1;
+      s.post_x = s.geom_w - s.post_x - s.post_w;
+    }
+    out[i] = s;
+  }
+  return MLXD_OK;
+}
+
+void source_rows(const DevSample& s, int32_t& r0, int32_t& r1) {
+  int64_t lo = 0, hi = s.pre_h;  // rows of the pre window
+  if (s.mode == kModeCopy) {
+    lo = s.post_y;
+    hi = (int64_t)s.post_y + s.post_h;
+  } else if (s.mode == kModeResize && s.pre_h != s.geom_h) {
+    const double ratio = (double)s.pre_h / (double)s.geom_h;
+    const double radius = ratio > 1.0 ? ratio : 1.0;
+    lo = (int64_t)std::floor((s.post_y + 0.5) * ratio - 0.5 - radius) - 2;
+    hi = (int64_t)std::ceil((s.post_y + s.post_h - 0.5) * ratio - 0.5 + radius) + 3;
+  } else if (s.mode == kModeResize) {
+    lo = s.post_y;
+    hi = (int64_t)s.post_y + s.post_h;
+  }
+  lo = std::max<int64_t>(lo, 0);
+  hi = std::min<int64_t>(hi, s.pre_h);
+  r0 = (int32_t)(s.pre_y + lo);
+  r1 = (int32_t)(s.pre_y + hi);
+}
+
+int get_lut(mlxd_ctx* ctx, const mlxd_batch_desc* b, int c_out, const float** lut) {
+  LutKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.c_out = c_out;
+  key.normalise = b->normalise ? 1 : 0;
+  std::memcpy(&key.divisor_bits, &b->divisor, 4);
+  if (key.normalise) {
+    std::memcpy(key.mean_bits, b->mean, 4 * c_out);
+    std::memcpy(key.std_bits, b->std_, 4 * c_out);
+  }
+  std::lock_guard<std::mutex> g(ctx->lut_mu);
+  auto it = ctx->luts.find(key);
+  if (it != ctx->luts.end()) {
+    *lut = it->second;
+    return MLXD_OK;
+  }
+  // Every entry is the chain of float32 operations numpy performs:
+  // float(v) / divisor, then - mean, then / std.
+  std::vector<float> table((size_t)c_out * 256);
+  for (int c = 0; c < c_out; c++) {
+    for (int v = 0; v < 256; v++) {
+      volatile float x = (float)v;
+      volatile float q = x / b->divisor;
+      if (key.normalise) {
+        volatile float t = q - b->mean[c];
+        q = t / b->std_[c];
+      }
+      table[(size_t)c * 256 + v] = q;
+    }
+  }
+  float* d = nullptr;
+  MLXD_CUDA(cudaMalloc(&d, table.size() * sizeof(float)));
+  cudaError_t e = cudaMemcpy(d, table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    cudaFree(d);
+    return fail_cuda(e, "cudaMemcpy(cast table)");
+  }
+  ctx->luts[key] = d;
+  *lut = d;
+  return MLXD_OK;
+}
+
+int prepare_launch(
+    mlxd_ctx* ctx, const mlxd_batch_desc* b, int n, LaunchParams& p) {
+  if (b->channels < 1 || b->channels > 4) {
+    return fail(MLXD_ERR_INVALID, "image: channels must be 0 < c <= 4");
+  }
+  if (b->gray && b->channels != 3) {
+    return fail(MLXD_ERR_INVALID, "image::channelReduction: expected a 3 channel uint8 array");
+  }
+  if (b->slot_h <= 0 || b->slot_w <= 0) {
+    return fail(MLXD_ERR_INVALID, "batch slot must have positive height and width");
+  }
+  if (b->out_dtype != MLXD_U8 && b->out_dtype != MLXD_F32) {
+    return fail(MLXD_ERR_INVALID, "unknown output dtype");
+  }
+  std::memset(&p, 0, sizeof(p));
+  p.n = n;
+  p.tiles_y = (b->slot_h + kTileH - 1) / kTileH;
+  p.tiles_x = (b->slot_w + kTileW - 1) / kTileW;
+  p.c_in = b->channels;
+  p.c_out = b->gray ? 1 : b->channels;
+  p.gray = b->gray ? 1 : 0;
+  p.gray_m[0] = b->gray_m[0];
+  p.gray_m[1] = b->gray_m[1];
+  p.gray_m[2] = b->gray_m[2];
+  p.gray_bias = b->gray_bias;
+  p.out_f32 = b->out_dtype == MLXD_F32;
+  p.pad_px = (int32_t)(uint8_t)(int32_t)b->pad_value;
+  p.status = ctx->d_status;
+  if (p.out_f32) {
+    if (!(b->divisor != 0.0f)) {
+      return fail(MLXD_ERR_INVALID, "cast divisor must be non-zero");
+    }
+    int rc = get_lut(ctx, b, p.c_out, &p.lut);
+    if (rc != MLXD_OK) {
+      return rc;
+    }
+  }
+  return MLXD_OK;
+}
+
+int enqueue_on_lane(
+    mlxd_ctx* ctx, Lane& lane, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch,
+    const std::vector<void*>* per_sample_dst) {
+  if (!samples || !batch || n < 0) {
+    return fail(MLXD_ERR_INVALID, "null descriptor or negative sample count");
+  }
+  if (n == 0) {
+    return MLXD_OK;
+  }
+  if (!batch->dst && !per_sample_dst) {
+    return fail(MLXD_ERR_INVALID, "null batch destination");
+  }
+  MLXD_CUDA(cudaSetDevice(ctx->device));
+  LaunchParams p;
+  int rc = prepare_launch(ctx, batch, n, p);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
+  std::vector<DevSample> dev;
+  bool any_resize = false;
+  rc = plan_samples(samples, n, batch, dev, any_resize);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
+  const size_t esize = p.out_f32 ? 4 : 1;
+  const size_t slot_bytes = (size_t)batch->slot_h * batch->slot_w * p.c_out * esize;
+  const size_t out_bytes = slot_bytes * n;
+  const bool host_src = batch->src_mem == MLXD_MEM_HOST;
+  const bool host_dst = batch->dst_mem == MLXD_MEM_HOST;
+  if (per_sample_dst && host_dst) {
+    return fail(MLXD_ERR_INVALID, "per-sample destinations must be device memory");
+  }
+
+  std::lock_guard<std::mutex> guard(lane.mu);
+  const int slot = lane.next_slot;
+  lane.next_slot = (slot + 1) % kDescSlots;
+  // The pinned descriptor table of this slot may still be in flight.
+  MLXD_CUDA(cudaEventSynchronize(lane.desc_copied[slot]));
+  rc = arena_reserve(ctx, lane.h_desc[slot], sizeof(DevSample) * n, true, lane.stream);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
+  rc = arena_reserve(ctx, lane.d_desc[slot], sizeof(DevSample) * n, false, lane.stream);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
+
+  // Stage host sources: only the rows the chain reads, each block 256-byte aligned.
+  struct Piece {
+    size_t offset, bytes;
+    const uint8_t* from;
+  };
+  std::vector<Piece> pieces;
+  size_t stage_bytes = 0;
+  if (host_src) {
+    pieces.resize(n);
+    for (int i = 0; i < n; i++) {
+      int32_t r0, r1;
+      source_rows(dev[i], r0, r1);
+      const size_t pitch = (size_t)dev[i].src_w * p.c_in;
+      pieces[i].offset = stage_bytes;
+      pieces[i].bytes = pitch * (size_t)(r1 - r0);
+      pieces[i].from = samples[i].src + pitch * (size_t)r0;
+      stage_bytes += (pieces[i].bytes + 255) & ~(size_t)255;
+    }
+    rc = arena_reserve(ctx, lane.d_src, stage_bytes + 256, false, lane.stream);
+    if (rc != MLXD_OK) {
+      return rc;
+    }
+    for (int i = 0; i < n; i++) {
+      int32_t r0, r1;
+      source_rows(dev[i], r0, r1);
+      const size_t pitch = (size_t)dev[i].src_w * p.c_in;
+      // Base of a virtual full image whose rows [r0, r1) are the staged block.
+      dev[i].src = static_cast<const uint8_t*>(lane.d_src.ptr) + pieces[i].offset - pitch * (size_t)r0;
+    }
+  }
+  uint8_t* out_base = static_cast<uint8_t*>(batch->dst);
+  if (host_dst) {
+    rc = arena_reserve(ctx, lane.d_out, out_bytes, false, lane.stream);
+    if (rc != MLXD_OK) {
+      return rc;
+    }
+    out_base = static_cast<uint8_t*>(lane.d_out.ptr);
+  }
+  for (int i = 0; i < n; i++) {
+    dev[i].dst = per_sample_dst ? (*per_sample_dst)[i] : static_cast<void*>(out_base + slot_bytes * i);
+  }
+
+  std::memcpy(lane.h_desc[slot].ptr, dev.data(), sizeof(DevSample) * n);
+  MLXD_CUDA(cudaMemcpyAsync(
+      lane.d_desc[slot].ptr, lane.h_desc[slot].ptr, sizeof(DevSample) * n, cudaMemcpyHostToDevice, lane.stream));
+  MLXD_CUDA(cudaEventRecord(lane.desc_copied[slot], lane.stream));
+  if (host_src) {
+    for (int i = 0; i < n; i++) {
+      MLXD_CUDA(cudaMemcpyAsync(
+          static_cast<uint8_t*>(lane.d_src.ptr) + pieces[i].offset, pieces[i].from, pieces[i].bytes,
+          cudaMemcpyHostToDevice, lane.stream));
+    }
+    ctx->h2d += stage_bytes;
+  }
+  p.samples = static_cast<const DevSample*>(lane.d_desc[slot].ptr);
+  MLXD_CUDA(launch_fused_batch(p, any_resize, lane.stream));
+  if (host_dst) {
+    MLXD_CUDA(cudaMemcpyAsync(batch->dst, lane.d_out.ptr, out_bytes, cudaMemcpyDeviceToHost, lane.stream));
+    ctx->d2h += out_bytes;
+  }
+  MLXD_CUDA(cudaMemcpyAsync(lane.h_status, ctx->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, lane.stream));
+  MLXD_CUDA(cudaEventRecord(lane.done, lane.stream));
+  ctx->batches += 1;
+  ctx->samples += n;
+  ctx->launches += 1;
+  return MLXD_OK;
+}
+
+int wait_lane(mlxd_ctx* ctx, Lane& lane, int timeout_ms) {
+  MLXD_CUDA(cudaSetDevice(ctx->device));
+  const auto start = std::chrono::steady_clock::now();
+  for (;;) {
+    cudaError_t e = cudaEventQuery(lane.done);
+    if (e == cudaSuccess) {
+      break;
+    }
+    if (e != cudaErrorNotReady) {
+      return fail_cuda(e, "cudaEventQuery(lane)");
+    }
+    if (timeout_ms >= 0) {
+      const auto el = std::chrono::duration_cast<std::chrono::milliseconds>(
+          std::chrono::steady_clock::now() - start).count();
+      if (el >= timeout_ms) {
+        return fail(MLXD_ERR_TIMEOUT, "lane still busy after " + std::to_string(timeout_ms) + " ms");
+      }
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(20));
+  }
+  if (*lane.h_status != 0) {
+    return fail(MLXD_ERR_DEVICE, "kernel self-check failed (status " + std::to_string(*lane.h_status) + ")");
+  }
+  return MLXD_OK;
+}
+
+} // namespace mlxd

@@ -1,0 +1,97 @@
+// Host-side state behind the C ABI: the context, its lanes and the code that
+// turns public descriptors into a launch.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/mlxd_b200.h"
+#include "fused_batch.h"
+
+namespace mlxd {
+
+const std::string& error_text();
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+int fail_cuda(cudaError_t e, const char* what);
+
+#define MLXD_CUDA(call)                       \
+  do {                                        \
+    cudaError_t e__ = (call);                 \
+    if (e__ != cudaSuccess) {                 \
+      return ::mlxd::fail_cuda(e__, #call);   \
+    }                                         \
+  } while (0)
+
+// Grow-only device or pinned-host buffer.
+struct Arena {
+  void* ptr = nullptr;
+  size_t cap = 0;
+};
+
+constexpr int kDescSlots = 4;
+
+struct Lane {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t done = nullptr;
+  Arena d_src;                        // staged sources
+  Arena d_out;                        // batch written by the kernel when dst is host memory
+  Arena d_desc[kDescSlots];           // DevSample tables
+  Arena h_desc[kDescSlots];           // their pinned images
+  cudaEvent_t desc_copied[kDescSlots] = {};
+  int next_slot = 0;
+  int32_t* h_status = nullptr;        // pinned copy of the device status word
+  std::mutex mu;                      // one caller at a time per lane
+};
+
+struct LutKey {
+  int32_t c_out, normalise;
+  uint32_t divisor_bits;
+  uint32_t mean_bits[4];
+  uint32_t std_bits[4];
+  bool operator<(const LutKey& o) const;
+};
+
+} // namespace mlxd
+
+struct mlxd_ctx {
+  int device = 0;
+  std::vector<mlxd::Lane*> lanes;     // n_lanes user lanes + one private lane for the synchronous ops
+  int n_user_lanes = 0;
+  int32_t* d_status = nullptr;
+  std::mutex lut_mu;
+  std::map<mlxd::LutKey, float*> luts;
+  std::atomic<uint64_t> batches{0}, samples{0}, launches{0}, h2d{0}, d2h{0}, reserved{0};
+};
+
+namespace mlxd {
+
+// Validate descriptors and build the device programs (src/dst pointers are
+// filled by the caller).  Returns MLXD_OK or an error with the message set.
+int plan_samples(
+    const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b,
+    std::vector<DevSample>& out, bool& any_resize);
+
+// Launch-wide parameters (cast table included) from a batch descriptor.
+int prepare_launch(mlxd_ctx* ctx, const mlxd_batch_desc* b, int n, LaunchParams& p);
+
+// Device cast table for a batch descriptor (cached per context).
+int get_lut(mlxd_ctx* ctx, const mlxd_batch_desc* b, int c_out, const float** lut);
+
+// Rows of a sample's source that its chain can read: [r0, r1).
+void source_rows(const DevSample& s, int32_t& r0, int32_t& r1);
+
+int arena_reserve(mlxd_ctx* ctx, Arena& a, size_t bytes, bool pinned, cudaStream_t stream_to_drain);
+
+int enqueue_on_lane(
+    mlxd_ctx* ctx, Lane& lane, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch,
+    const std::vector<void*>* per_sample_dst);
+
+int wait_lane(mlxd_ctx* ctx, Lane& lane, int timeout_ms);
+
+} // namespace mlxd

@@ -1,0 +1,71 @@
+// Device-side layout of one fused batch launch: the per-sample programs the
+// kernel executes and the launch-wide parameters.  Host code fills these from
+// the public descriptors (include/mlxd_b200.h) after validating them.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mlxd {
+
+constexpr int kTileH = 16;    // output rows per CTA
+constexpr int kTileW = 64;    // output pixels per row per CTA
+constexpr int kThreads = 256;
+
+// Shared-memory budget of the resize path (bytes / floats).  Two CTAs of this
+// size fit in one SM's 227 KB.
+constexpr int kSrcTileBytes = 36 * 1024;   // staged source footprint, uint8
+constexpr int kMidFloats = 10 * 1024;      // vertically filtered rows, float32
+constexpr int kWeightFloats = 2 * 1024;    // tap weights of both axes
+
+enum Mode : int32_t { kModeCopy = 0, kModeResize = 1, kModeAffine = 2 };
+
+// One sample's program.  Coordinates name four nested images:
+//   source [src_h, src_w] -> pre window [pre_h, pre_w] (+mirror)
+//   -> geometric output [geom_h, geom_w] -> post window [post_h, post_w] (+mirror)
+// and the post window lands in the top-left corner of the slot [slot_h, slot_w].
+struct __align__(16) DevSample {
+  const uint8_t* src;
+  void* dst;
+  int32_t src_h, src_w;
+  int32_t pre_x, pre_y, pre_w, pre_h;
+  int32_t geom_w, geom_h;
+  int32_t post_x, post_y, post_w, post_h;
+  int32_t slot_h, slot_w;
+  int32_t mode;
+  int32_t pre_flip, post_flip;
+  int32_t sub_h, sub_w;   // resize: geometric-output rows / columns filtered per pass
+  int32_t cap_y, cap_x;   // resize: tap-count bound per axis
+  float mx[6];
+  int32_t pad_[3];
+};
+
+struct LaunchParams {
+  const DevSample* samples;
+  int32_t n;
+  int32_t tiles_y, tiles_x;   // tile grid of the largest slot
+  int32_t c_in;               // channels of every source
+  int32_t c_out;              // 1 when gray, else c_in
+  int32_t gray;
+  int32_t gray_m[3];
+  int32_t gray_bias;
+  int32_t out_f32;
+  const float* lut;           // [c_out][256] cast table, device
+  int32_t pad_px;             // pad value as a pixel
+  int32_t* status;            // device word, non-zero once a self-check failed
+};
+
+// Bytes of dynamic shared memory the kernel needs for these parameters.
+size_t fused_batch_smem_bytes(const LaunchParams& p, bool any_resize);
+
+cudaError_t launch_fused_batch(const LaunchParams& p, bool any_resize, cudaStream_t stream);
+
+// Conservative footprint check used by the host planner: can one pass over
+// sub_h x sub_w geometric-output pixels be staged for this axis pair?
+struct AxisPlan {
+  int32_t cap;      // tap-count bound
+  int32_t extent;   // bound on source samples touched by `sub` outputs
+};
+AxisPlan plan_axis(int32_t n_src, int32_t n_dst, int32_t sub);
+
+} // namespace mlxd
