@@ -1,0 +1,172 @@
+#include "mlx/data/core/Batcher.h"
+
+#include <map>
+#include <stdexcept>
+
+#include "mlx/data/core/Utils.h"
+
+namespace mlx {
+namespace data {
+namespace core {
+
+namespace {
+
+// A sample whose image entries may still be programs rather than pixels.
+struct Entry {
+  std::shared_ptr<Array> array;            // set when concrete
+  std::shared_ptr<gpu::LazyImage> lazy;    // set when pending
+};
+using LazySample = std::unordered_map<std::string, Entry>;
+
+bool gpu_image(const std::shared_ptr<Array>& a) {
+  return a && a->type() == UInt8 && a->ndim() == 3 && a->shape(2) >= 1 && a->shape(2) <= 4 && a->size() > 0;
+}
+
+void run_op(LazySample& s, const op::ImageTransformOp& op) {
+  auto it = s.find(op.input_key());
+  if (it == s.end()) {
+    throw std::runtime_error("key <" + op.input_key() + "> expected");
+  }
+  Entry in = it->second;
+  Entry out;
+  if (!in.lazy && !gpu_image(in.array)) {
+    // videos, non-uint8 arrays, malformed images: the op decides (and throws)
+    out.array = op.apply_key(in.array);
+  } else {
+    auto lazy = in.lazy ? std::make_shared<gpu::LazyImage>(*in.lazy) : std::make_shared<gpu::LazyImage>(in.array);
+    Sample concrete_entries;
+    if (op.reads_sample()) {
+      for (auto& kv : s) {
+        if (kv.second.array) {
+          concrete_entries[kv.first] = kv.second.array;
+        }
+      }
+    }
+    if (!op.fold_in(*lazy, concrete_entries)) {
+      // the program is full: compute what we have, start a new one
+      auto pixels = (in.lazy ? *in.lazy : gpu::LazyImage(in.array)).materialise();
+      lazy = std::make_shared<gpu::LazyImage>(pixels);
+      if (!op.fold_in(*lazy, concrete_entries)) {
+        throw std::runtime_error("ImageTransformOp: internal error: op does not fold into an empty program");
+      }
+    }
+    out.lazy = lazy;
+  }
+  s[op.output_key()] = out;
+}
+
+std::shared_ptr<Array> concrete(const Entry& e) {
+  if (e.array) {
+    return e.array;
+  }
+  if (e.lazy->untouched()) {
+    return std::make_shared<Array>(e.lazy->source());
+  }
+  return e.lazy->materialise();
+}
+
+} // namespace
+
+Batcher::Batcher(
+    std::vector<std::shared_ptr<op::ImageTransformOp>> ops,
+    std::unordered_map<std::string, double> pad_values,
+    std::unordered_map<std::string, int> batch_dims,
+    std::vector<CastRequest> casts)
+    : ops_(std::move(ops)),
+      pad_values_(std::move(pad_values)),
+      batch_dims_(std::move(batch_dims)),
+      casts_(std::move(casts)) {}
+
+Sample Batcher::run(const std::vector<Sample>& raw) const {
+  if (raw.empty()) {
+    return Sample();
+  }
+  // 1. symbolic execution, sample-major like a pull pipeline
+  std::vector<LazySample> lazy(raw.size());
+  for (size_t i = 0; i < raw.size(); i++) {
+    for (auto& kv : raw[i]) {
+      lazy[i][kv.first].array = kv.second;
+    }
+    for (auto& op : ops_) {
+      run_op(lazy[i], *op);
+    }
+  }
+  // 2. per key of the first sample: one batch tensor
+  Sample out;
+  for (auto& first_kv : lazy.front()) {
+    const std::string& key = first_kv.first;
+    std::vector<Entry> col;
+    col.reserve(lazy.size());
+    for (auto& s : lazy) {
+      auto it = s.find(key);
+      if (it == s.end()) {
+        throw std::runtime_error("mergeBatch: inconsistent sample keys in batch (unknown key: <" + key + ">)");
+      }
+      col.push_back(it->second);
+    }
+    double pad = 0.0;
+    if (auto p = pad_values_.find(key); p != pad_values_.end()) {
+      pad = p->second;
+    }
+    const auto dim = batch_dims_.find(key);
+    bool on_gpu = dim == batch_dims_.end();
+    for (auto& e : col) {
+      on_gpu = on_gpu && (e.lazy || gpu_image(e.array));
+    }
+    if (on_gpu) {
+      std::vector<gpu::LazyImage> images;
+      images.reserve(col.size());
+      bool same = true;
+      for (auto& e : col) {
+        images.push_back(e.lazy ? *e.lazy : gpu::LazyImage(e.array));
+        same = same && images.back().source_channels() == images.front().source_channels() &&
+            images.back().is_gray() == images.front().is_gray();
+      }
+      if (!same) {
+        throw std::runtime_error("BatchShape: batched arrays expected to have consistent shapes");
+      }
+      bool replaced = false;
+      for (auto& c : casts_) {
+        if (c.ikey != key) {
+          continue;
+        }
+        auto f32 = gpu::Runtime::get().batch(images, pad, &c.spec);
+        if (c.okey.empty() || c.okey == key) {
+          out[key] = f32;
+          replaced = true;
+        } else {
+          out[c.okey] = f32;
+        }
+      }
+      if (!replaced) {
+        out[key] = gpu::Runtime::get().batch(images, pad, nullptr);
+      }
+      continue;
+    }
+    std::vector<std::shared_ptr<Array>> arrs;
+    arrs.reserve(col.size());
+    for (auto& e : col) {
+      arrs.push_back(concrete(e));
+    }
+    std::shared_ptr<Array> merged =
+        dim == batch_dims_.end() ? array::batch(arrs, pad) : array::batch(arrs, dim->second, pad);
+    out[key] = merged;
+    for (auto& c : casts_) {
+      if (c.ikey == key) {
+        out[c.okey.empty() ? key : c.okey] = gpu::Runtime::get().cast(merged, c.spec);
+      }
+    }
+  }
+  return out;
+}
+
+Sample merge_batch(
+    const std::vector<Sample>& samples,
+    const std::unordered_map<std::string, double>& pad_values,
+    const std::unordered_map<std::string, int>& batch_dims) {
+  return Batcher({}, pad_values, batch_dims).run(samples);
+}
+
+} // namespace core
+} // namespace data
+} // namespace mlx

@@ -1,0 +1,364 @@
+#include "mlx/data/gpu/Runtime.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <stdexcept>
+#include <string>
+
+namespace mlx {
+namespace data {
+namespace gpu {
+
+namespace {
+int g_device = -1;
+
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  if (!v || !*v) {
+    return fallback;
+  }
+  return std::atoi(v);
+}
+
+int32_t to_i32(int64_t v, const char* what) {
+  if (v < 0 || v > 0x7fffffffLL) {
+    throw std::runtime_error(std::string("image: ") + what + " out of range");
+  }
+  return static_cast<int32_t>(v);
+}
+} // namespace
+
+// ---------------------------------------------------------------- Window
+void Window::crop(int64_t cx, int64_t cy, int64_t cw, int64_t ch) {
+  // Same checks as array::sub on the materialised image.
+  if (cx < 0 || cy < 0 || cx >= w || cy >= h) {
+    throw std::runtime_error("Array: sub: offset out of bound");
+  }
+  if (cx + cw > w || cy + ch > h) {
+    throw std::runtime_error("Array: sub: shape out of bound");
+  }
+  x += flip ? (w - cx - cw) : cx;
+  y += cy;
+  w = cw;
+  h = ch;
+}
+
+// ---------------------------------------------------------------- LazyImage
+LazyImage::LazyImage(const std::shared_ptr<const Array>& src) : src_(src) {
+  if (src->ndim() != 3) {
+    throw std::runtime_error("verifyImage: image must be 3 dimension Array (HWC)");
+  }
+  channels_ = src->shape(2);
+  if (channels_ == 0 || channels_ > 4) {
+    throw std::runtime_error("verifyImage: channels must be 0 <= c <= 4");
+  }
+  pre_.w = src->shape(1);
+  pre_.h = src->shape(0);
+  geom_w_ = pre_.w;
+  geom_h_ = pre_.h;
+  post_ = Window{0, 0, pre_.w, pre_.h, false};
+}
+
+int64_t LazyImage::width() const {
+  return post_.w;
+}
+
+int64_t LazyImage::height() const {
+  return post_.h;
+}
+
+void LazyImage::crop(int64_t x, int64_t y, int64_t w, int64_t h) {
+  if (w <= 0 || h <= 0) {
+    throw std::runtime_error("image: cannot create image with 0 or negative dimension");
+  }
+  if (geom_ == MLXD_GEOM_NONE) {
+    pre_.crop(x, y, w, h);
+    geom_w_ = pre_.w;
+    geom_h_ = pre_.h;
+    post_ = Window{0, 0, pre_.w, pre_.h, false};
+  } else {
+    post_.crop(x, y, w, h);
+  }
+  untouched_ = false;
+}
+
+void LazyImage::hflip() {
+  if (geom_ == MLXD_GEOM_NONE) {
+    pre_.flip = !pre_.flip;
+  } else {
+    post_.flip = !post_.flip;
+  }
+  untouched_ = false;
+}
+
+bool LazyImage::resize(int64_t dw, int64_t dh) {
+  if (geom_ != MLXD_GEOM_NONE || gray_) {
+    return false;
+  }
+  if (src_->type() != UInt8) {
+    throw std::invalid_argument("image must be of type UInt8");
+  }
+  if (dh <= 0 || dw <= 0) {
+    throw std::runtime_error("image: cannot create image with 0 or negative dimension");
+  }
+  geom_ = MLXD_GEOM_RESIZE;
+  geom_w_ = dw;
+  geom_h_ = dh;
+  post_ = Window{0, 0, dw, dh, false};
+  untouched_ = false;
+  return true;
+}
+
+bool LazyImage::affine(const float mx[6], int64_t tw, int64_t th) {
+  if (geom_ != MLXD_GEOM_NONE || gray_) {
+    return false;
+  }
+  if (src_->type() != UInt8) {
+    throw std::invalid_argument("image must be of type UInt8");
+  }
+  if (th <= 0 || tw <= 0) {
+    throw std::runtime_error("image: cannot create image with 0 or negative dimension");
+  }
+  geom_ = MLXD_GEOM_AFFINE;
+  geom_w_ = tw;
+  geom_h_ = th;
+  std::memcpy(mx_, mx, sizeof(mx_));
+  post_ = Window{0, 0, tw, th, false};
+  untouched_ = false;
+  return true;
+}
+
+bool LazyImage::channel_reduction(float bias, const float m[3]) {
+  if (channels() != 3) {
+    throw std::runtime_error("image::channelReduction: expected a 3 channel uint8 array");
+  }
+  if (src_->type() != UInt8) {
+    throw std::invalid_argument("image must be of type UInt8");
+  }
+  // 16.16 fixed point, truncated: float coefficient times the int scale
+  // (mlx/data/core/image/ImageTransform.cpp:159-164).
+  const int scale = 256 * 256;
+  gray_bias_ = static_cast<int>(bias * scale);
+  for (int i = 0; i < 3; i++) {
+    gray_m_[i] = static_cast<int>(m[i] * scale);
+  }
+  gray_ = true;
+  untouched_ = false;
+  return true;
+}
+
+void LazyImage::gray_params(int32_t m[3], int32_t& bias) const {
+  std::memcpy(m, gray_m_, sizeof(gray_m_));
+  bias = gray_bias_;
+}
+
+void LazyImage::describe(mlxd_sample_desc& d) const {
+  std::memset(&d, 0, sizeof(d));
+  d.src = static_cast<const uint8_t*>(src_->data());
+  d.src_h = to_i32(src_->shape(0), "height");
+  d.src_w = to_i32(src_->shape(1), "width");
+  d.pre_x = to_i32(pre_.x, "crop offset");
+  d.pre_y = to_i32(pre_.y, "crop offset");
+  d.pre_w = to_i32(pre_.w, "crop width");
+  d.pre_h = to_i32(pre_.h, "crop height");
+  d.pre_flip = pre_.flip ? 1 : 0;
+  d.geom = geom_;
+  d.geom_w = to_i32(geom_w_, "target width");
+  d.geom_h = to_i32(geom_h_, "target height");
+  std::memcpy(d.mx, mx_, sizeof(mx_));
+  d.post_x = to_i32(post_.x, "crop offset");
+  d.post_y = to_i32(post_.y, "crop offset");
+  d.post_w = to_i32(post_.w, "crop width");
+  d.post_h = to_i32(post_.h, "crop height");
+  d.post_flip = post_.flip ? 1 : 0;
+}
+
+std::shared_ptr<Array> LazyImage::materialise() const {
+  std::vector<LazyImage> one{*this};
+  auto batched = Runtime::get().batch(one, 0.0, nullptr);
+  // drop the leading batch dimension; storage is shared
+  return std::make_shared<Array>(
+      batched->type(), std::vector<int64_t>{batched->shape(1), batched->shape(2), batched->shape(3)},
+      batched->storage());
+}
+
+// ---------------------------------------------------------------- Runtime
+Runtime& Runtime::get() {
+  static Runtime* rt = new Runtime();  // never destroyed: arrays may outlive static teardown
+  return *rt;
+}
+
+void Runtime::set_device(int device) {
+  g_device = device;
+}
+
+int Runtime::device() {
+  if (g_device < 0) {
+    g_device = env_int("MLXD_DEVICE", env_int("LOCAL_RANK", 0));
+  }
+  return g_device;
+}
+
+void Runtime::check(int rc) const {
+  if (rc == MLXD_OK) {
+    return;
+  }
+  const std::string msg = mlxd_last_error();
+  if (rc == MLXD_ERR_INVALID) {
+    throw std::runtime_error(msg);
+  }
+  throw std::runtime_error("mlx-data GPU path: " + msg);
+}
+
+mlxd_ctx* Runtime::ctx() {
+  std::lock_guard<std::mutex> g(mu_);
+  if (!ctx_) {
+    n_lanes_ = std::max(1, env_int("MLXD_LANES", 8));
+    const long long gib = env_int("MLXD_PINNED_POOL_GIB", 16);
+    pool_limit_ = static_cast<size_t>(gib) << 30;
+    mlxd_ctx* c = nullptr;
+    const int rc = mlxd_ctx_create(device(), n_lanes_, &c);
+    if (rc != MLXD_OK) {
+      throw std::runtime_error(
+          std::string("mlx-data GPU path: cannot create a CUDA context (there is no CPU fallback): ") +
+          mlxd_last_error());
+    }
+    ctx_ = c;
+  }
+  return ctx_;
+}
+
+int Runtime::lane() {
+  static thread_local int mine = -1;
+  if (mine < 0) {
+    ctx();
+    std::lock_guard<std::mutex> g(mu_);
+    mine = next_lane_++ % n_lanes_;
+  }
+  return mine;
+}
+
+Runtime::~Runtime() {}
+
+void* Runtime::pool_take(size_t bytes, size_t& held) {
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = pool_.lower_bound(bytes);
+  // reuse a block that is at most 25% larger than asked for
+  if (it != pool_.end() && it->first <= bytes + bytes / 4) {
+    void* p = it->second;
+    held = it->first;
+    pool_bytes_ -= it->first;
+    pool_.erase(it);
+    return p;
+  }
+  return nullptr;
+}
+
+void Runtime::pool_give(void* p, size_t bytes) {
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    if (pool_bytes_ + bytes <= pool_limit_) {
+      pool_.emplace(bytes, p);
+      pool_bytes_ += bytes;
+      return;
+    }
+  }
+  mlxd_pinned_free(p);
+}
+
+std::shared_ptr<Array> Runtime::pinned_array(ArrayType type, const std::vector<int64_t>& shape) {
+  ctx();
+  int64_t n = array_type_size(type);
+  for (auto d : shape) {
+    n *= d;
+  }
+  size_t bytes = static_cast<size_t>(std::max<int64_t>(n, 1));
+  bytes = (bytes + 4095) & ~size_t(4095);
+  size_t held = bytes;  // a recycled block goes back under the size it was allocated with
+  void* p = pool_take(bytes, held);
+  if (!p) {
+    p = mlxd_pinned_alloc(bytes);
+    if (!p) {
+      throw std::runtime_error(std::string("mlx-data GPU path: ") + mlxd_last_error());
+    }
+  }
+  Runtime* self = this;
+  std::shared_ptr<void> storage(p, [self, held](void* q) { self->pool_give(q, held); });
+  return std::make_shared<Array>(type, shape, storage);
+}
+
+std::shared_ptr<Array> Runtime::batch(const std::vector<LazyImage>& images, double pad_value, const CastSpec* cast) {
+  if (images.empty()) {
+    throw std::runtime_error("Array: cannot batch an empty list of arrays");
+  }
+  const int n = static_cast<int>(images.size());
+  const LazyImage& first = images.front();
+  int64_t max_h = 0, max_w = 0;
+  std::vector<mlxd_sample_desc> descs(images.size());
+  for (int i = 0; i < n; i++) {
+    const LazyImage& im = images[i];
+    if (im.source()->type() != UInt8) {
+      throw std::invalid_argument("image must be of type UInt8");
+    }
+    if (im.source_channels() != first.source_channels() || im.is_gray() != first.is_gray()) {
+      throw std::runtime_error("BatchShape: batched arrays expected to have consistent shapes");
+    }
+    im.describe(descs[i]);
+    max_h = std::max(max_h, im.height());
+    max_w = std::max(max_w, im.width());
+  }
+  mlxd_batch_desc b;
+  std::memset(&b, 0, sizeof(b));
+  b.slot_h = to_i32(max_h, "height");
+  b.slot_w = to_i32(max_w, "width");
+  b.channels = static_cast<int32_t>(first.source_channels());
+  if (first.is_gray()) {
+    b.gray = 1;
+    first.gray_params(b.gray_m, b.gray_bias);
+  }
+  b.pad_value = pad_value;
+  b.src_mem = MLXD_MEM_HOST;
+  b.dst_mem = MLXD_MEM_HOST;
+  b.divisor = 1.0f;
+  ArrayType out_type = UInt8;
+  if (cast) {
+    out_type = Float;
+    b.out_dtype = MLXD_F32;
+    b.divisor = cast->divisor;
+    b.normalise = cast->normalise ? 1 : 0;
+    std::memcpy(b.mean, cast->mean, sizeof(b.mean));
+    std::memcpy(b.std_, cast->std_, sizeof(b.std_));
+  }
+  auto out = pinned_array(out_type, {n, max_h, max_w, first.channels()});
+  b.dst = out->data();
+  mlxd_ctx* c = ctx();
+  const int ln = lane();
+  check(mlxd_fused_batch(c, ln, descs.data(), n, &b));
+  check(mlxd_batch_wait(c, ln, -1));
+  return out;
+}
+
+std::shared_ptr<Array> Runtime::cast(const std::shared_ptr<const Array>& arr, const CastSpec& spec) {
+  if (arr->type() != UInt8) {
+    throw std::invalid_argument("cast: array must be of type UInt8");
+  }
+  if (arr->ndim() < 1 || arr->shape(arr->ndim() - 1) < 1 || arr->shape(arr->ndim() - 1) > 4) {
+    throw std::runtime_error("cast: the last dimension must hold 1 to 4 channels");
+  }
+  const int c = static_cast<int>(arr->shape(arr->ndim() - 1));
+  auto out = pinned_array(Float, arr->shape());
+  if (arr->size() == 0) {
+    return out;
+  }
+  check(mlxd_cast_scale_normalise(
+      ctx(), static_cast<const uint8_t*>(arr->data()), arr->size() / c, c, spec.divisor,
+      spec.normalise ? spec.mean : nullptr, spec.normalise ? spec.std_ : nullptr,
+      static_cast<float*>(out->data())));
+  return out;
+}
+
+} // namespace gpu
+} // namespace data
+} // namespace mlx

@@ -1,0 +1,122 @@
+// Bridge between the C++ pipeline and the CUDA library's C ABI
+// (include/mlxd_b200.h): the process-wide context, page-locked Array storage,
+// and LazyImage - an image described by a source array plus the op chain
+// still to be run on it, so that a whole batch becomes one kernel launch.
+#pragma once
+
+#include <cstdint>
+#include <memory>
+#include <mutex>
+#include <map>
+#include <vector>
+
+#include "mlx/data/Array.h"
+#include "mlxd_b200.h"
+
+namespace mlx {
+namespace data {
+namespace gpu {
+
+// The uint8 -> float32 cast fused after batching: x / divisor, optionally
+// (x / divisor - mean[c]) / std[c] - numpy's float32 arithmetic for
+// x.astype("float32") / 255 and its normalised form.
+struct CastSpec {
+  float divisor = 255.0f;
+  bool normalise = false;
+  float mean[4] = {0, 0, 0, 0};
+  float std_[4] = {1, 1, 1, 1};
+};
+
+// Axis-aligned window of an image, optionally mirrored left-right.
+struct Window {
+  int64_t x = 0, y = 0, w = 0, h = 0;
+  bool flip = false;
+  // Crop the (possibly mirrored) window in its own coordinates.
+  void crop(int64_t cx, int64_t cy, int64_t cw, int64_t ch);
+};
+
+class LazyImage {
+ public:
+  // Checks that src looks like an image the way core::image::verify_image does.
+  explicit LazyImage(const std::shared_ptr<const Array>& src);
+
+  int64_t width() const;
+  int64_t height() const;
+  int64_t channels() const { return gray_ ? 1 : channels_; }
+  int64_t source_channels() const { return channels_; }
+  bool is_gray() const { return gray_; }
+  // True while no op has been folded in: the result is the source itself.
+  bool untouched() const { return untouched_; }
+  const std::shared_ptr<const Array>& source() const { return src_; }
+
+  void crop(int64_t x, int64_t y, int64_t w, int64_t h);
+  void hflip();
+  // These return false when the op cannot join the program already recorded
+  // (a second geometric op, or a geometric op after the channel reduction);
+  // the caller then materialises and starts a new LazyImage.
+  bool resize(int64_t dw, int64_t dh);
+  bool affine(const float mx[6], int64_t tw, int64_t th);
+  bool channel_reduction(float bias, const float m[3]);
+
+  void describe(mlxd_sample_desc& d) const;
+  void gray_params(int32_t m[3], int32_t& bias) const;
+
+  // Run the recorded program now: a uint8 [h, w, channels()] array.
+  std::shared_ptr<Array> materialise() const;
+
+ private:
+  std::shared_ptr<const Array> src_;
+  int64_t channels_ = 0;
+  Window pre_, post_;
+  int geom_ = MLXD_GEOM_NONE;
+  int64_t geom_w_ = 0, geom_h_ = 0;
+  float mx_[6] = {0, 0, 0, 0, 0, 0};
+  bool gray_ = false;
+  int32_t gray_m_[3] = {0, 0, 0};
+  int32_t gray_bias_ = 0;
+  bool untouched_ = true;
+};
+
+class Runtime {
+ public:
+  static Runtime& get();
+
+  // Choose the CUDA device before the first GPU call (default: environment
+  // MLXD_DEVICE, then LOCAL_RANK, then 0).
+  static void set_device(int device);
+  static int device();
+
+  mlxd_ctx* ctx();
+  // Lane of the calling thread: threads are spread round-robin over lanes.
+  int lane();
+  void check(int rc) const;
+
+  // Array whose storage is page-locked host memory from a recycling pool.
+  std::shared_ptr<Array> pinned_array(ArrayType type, const std::vector<int64_t>& shape);
+
+  // One fused launch: every image's program, batch + pad, optional cast.
+  // Result is [N, max_h, max_w, C] uint8, or float32 when cast is given.
+  std::shared_ptr<Array> batch(const std::vector<LazyImage>& images, double pad_value, const CastSpec* cast);
+
+  // Cast an existing uint8 array (any shape, last dimension = channels <= 4).
+  std::shared_ptr<Array> cast(const std::shared_ptr<const Array>& arr, const CastSpec& spec);
+
+  ~Runtime();
+
+ private:
+  Runtime() = default;
+  void* pool_take(size_t bytes, size_t& held);
+  void pool_give(void* p, size_t bytes);
+
+  std::mutex mu_;
+  mlxd_ctx* ctx_ = nullptr;
+  int n_lanes_ = 8;
+  int next_lane_ = 0;
+  std::multimap<size_t, void*> pool_;
+  size_t pool_bytes_ = 0;
+  size_t pool_limit_ = size_t(16) << 30;
+};
+
+} // namespace gpu
+} // namespace data
+} // namespace mlx

@@ -1,0 +1,420 @@
+// pybind11 module `_c`: the Python face of the C++ pipeline, with the class,
+// method and keyword names of mlx-data's bindings (python/src/wrap_stream.cpp,
+// wrap_buffer.cpp, wrap_dataset.h, wrap_core.cpp) for the ops on the
+// image-transform-and-batch path.  Arrays cross the boundary without a copy in
+// both directions; every call into the pipeline releases the GIL and Python
+// callbacks take it back.
+#include <pybind11/functional.h>
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <optional>
+#include <sstream>
+
+#include "mlx/data/Buffer.h"
+#include "mlx/data/Stream.h"
+#include "mlx/data/core/State.h"
+#include "mlx/data/gpu/Runtime.h"
+
+namespace py = pybind11;
+using namespace mlx::data;
+
+namespace {
+
+// Delete pipeline objects without the GIL: their destructors may join worker
+// threads that are waiting for it.
+template <class T>
+struct ReleaseGilDeleter {
+  void operator()(T* p) const {
+    py::gil_scoped_release nogil;
+    delete p;
+  }
+};
+
+ArrayType dtype_to_type(const py::dtype& dt) {
+  const char kind = dt.kind();
+  const auto size = dt.itemsize();
+  if (kind == 'u' && size == 1) return UInt8;
+  if ((kind == 'i' && size == 1) || kind == 'S') return Int8;
+  if (kind == 'i' && size == 4) return Int32;
+  if (kind == 'i' && size == 8) return Int64;
+  if (kind == 'f' && size == 4) return Float;
+  if (kind == 'f' && size == 8) return Double;
+  throw std::invalid_argument(
+      "[to_array] Unsupported dtype " + std::string(py::str(dt)) +
+      " (uint8, int8, int32, int64, float32 and float64 are accepted)");
+}
+
+// numpy -> Array, sharing memory.  The Array holds a reference to the numpy
+// object and drops it under the GIL.
+std::shared_ptr<Array> wrap_numpy(py::array a) {
+  if (!(a.flags() & py::array::c_style)) {
+    throw std::runtime_error("[to_array] Contiguous array expected -- use numpy.ascontiguousarray()");
+  }
+  const ArrayType type = dtype_to_type(a.dtype());
+  std::vector<int64_t> shape(a.shape(), a.shape() + a.ndim());
+  if (a.dtype().kind() == 'S') {
+    shape.push_back(a.dtype().itemsize());
+  }
+  PyObject* keep = a.inc_ref().ptr();
+  std::shared_ptr<void> storage(const_cast<void*>(a.data()), [keep](void*) {
+    py::gil_scoped_acquire gil;
+    Py_DECREF(keep);
+  });
+  return std::make_shared<Array>(type, shape, storage);
+}
+
+std::shared_ptr<Array> to_array(py::handle obj) {
+  if (py::isinstance<py::array>(obj)) {
+    return wrap_numpy(py::reinterpret_borrow<py::array>(obj));
+  }
+  if (py::isinstance<py::bool_>(obj) || py::isinstance<py::int_>(obj)) {
+    return std::make_shared<Array>(obj.cast<int64_t>());
+  }
+  if (py::isinstance<py::float_>(obj)) {
+    return std::make_shared<Array>(obj.cast<double>());
+  }
+  if (py::isinstance<py::bytes>(obj)) {
+    return std::make_shared<Array>(obj.cast<std::string>());
+  }
+  if (py::isinstance<py::str>(obj)) {
+    throw std::invalid_argument(
+        "[to_array] Cannot convert strings to arrays. Please encode them as bytes first.");
+  }
+  // anything else: let numpy interpret it, then copy (the temporary is ours)
+  py::array converted;
+  try {
+    converted = py::array::ensure(obj, py::array::c_style);
+  } catch (...) {
+    converted = py::array();
+  }
+  if (!converted || converted.dtype().kind() == 'O') {
+    PyErr_Clear();
+    throw std::invalid_argument(
+        "[to_array] Cannot convert type " + std::string(py::str(py::type::of(obj))) +
+        " to an array. Use a numpy array, a python buffer or scalar.");
+  }
+  return array::clone(wrap_numpy(converted));
+}
+
+py::array to_numpy(const std::shared_ptr<const Array>& a) {
+  if (!a) {
+    throw std::runtime_error("Stream: empty value in sample");
+  }
+  const char* fmt = nullptr;
+  switch (a->type()) {
+    case Int8: fmt = "i1"; break;
+    case UInt8: fmt = "u1"; break;
+    case Int32: fmt = "i4"; break;
+    case Int64: fmt = "i8"; break;
+    case Float: fmt = "f4"; break;
+    case Double: fmt = "f8"; break;
+    default: throw std::runtime_error("internal error: unknown type");
+  }
+  // the capsule owns one shared_ptr and so keeps the storage alive
+  auto* holder = new std::shared_ptr<const Array>(a);
+  py::capsule owner(holder, [](void* p) { delete static_cast<std::shared_ptr<const Array>*>(p); });
+  std::vector<py::ssize_t> shape(a->shape().begin(), a->shape().end());
+  std::vector<py::ssize_t> strides(shape.size());
+  py::ssize_t step = static_cast<py::ssize_t>(a->itemsize());
+  for (int d = static_cast<int>(shape.size()) - 1; d >= 0; d--) {
+    strides[d] = step;
+    step *= shape[d];
+  }
+  return py::array(py::dtype(fmt), shape, strides, a->data(), owner);
+}
+
+py::dict to_py_sample(const Sample& s) {
+  py::dict d;
+  for (auto& kv : s) {
+    d[py::str(kv.first)] = to_numpy(kv.second);
+  }
+  return d;
+}
+
+Sample to_sample(const py::dict& d) {
+  Sample s;
+  for (auto item : d) {
+    s[item.first.cast<std::string>()] = to_array(item.second);
+  }
+  return s;
+}
+
+gpu::CastSpec make_cast(const std::string& dtype, double scale, const std::optional<std::vector<float>>& mean,
+                        const std::optional<std::vector<float>>& std_) {
+  if (dtype != "float32") {
+    throw std::invalid_argument("key_cast: only dtype=\"float32\" is available");
+  }
+  if (mean.has_value() != std_.has_value()) {
+    throw std::invalid_argument("key_cast: mean and std must be given together");
+  }
+  gpu::CastSpec spec;
+  spec.divisor = static_cast<float>(scale);
+  if (mean) {
+    if (mean->size() != std_->size() || mean->empty() || mean->size() > 4) {
+      throw std::invalid_argument("key_cast: mean and std need one value per channel (1 to 4)");
+    }
+    spec.normalise = true;
+    for (size_t i = 0; i < 4; i++) {
+      // a single value applies to every channel
+      spec.mean[i] = (*mean)[mean->size() == 1 ? 0 : std::min(i, mean->size() - 1)];
+      spec.std_[i] = (*std_)[std_->size() == 1 ? 0 : std::min(i, std_->size() - 1)];
+    }
+  }
+  return spec;
+}
+
+template <class T, class PyClass>
+void bind_ops(PyClass& c) {
+  using nogil = py::call_guard<py::gil_scoped_release>;
+  const char* okd = "output_key";
+  c.def("image_center_crop", &T::image_center_crop, nogil(), py::arg("key"), py::arg("w"), py::arg("h"),
+        py::arg(okd) = "", "Center crop the image at ``key`` to ``w`` x ``h``.");
+  c.def("image_center_crop_if", &T::image_center_crop_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("w"),
+        py::arg("h"), py::arg(okd) = "");
+  c.def("image_channel_reduction", &T::image_channel_reduction, nogil(), py::arg("key"),
+        py::arg("preset") = "default", py::arg(okd) = "",
+        "Reduce an RGB image to one channel with a named luma mix (default, rec601, rec709, rec2020, green).");
+  c.def("image_channel_reduction_if", &T::image_channel_reduction_if, nogil(), py::arg("cond"), py::arg("key"),
+        py::arg("preset") = "default", py::arg(okd) = "");
+  c.def("image_random_area_crop", &T::image_random_area_crop, nogil(), py::arg("key"), py::arg("area_range"),
+        py::arg("aspect_ratio_range"), py::arg("num_trial") = 10, py::arg(okd) = "",
+        "Crop a random rectangle whose area fraction and aspect ratio fall in the given ranges.");
+  c.def("image_random_area_crop_if", &T::image_random_area_crop_if, nogil(), py::arg("cond"), py::arg("key"),
+        py::arg("area_range"), py::arg("aspect_ratio_range"), py::arg("num_trial") = 10, py::arg(okd) = "");
+  c.def("image_random_crop", &T::image_random_crop, nogil(), py::arg("key"), py::arg("w"), py::arg("h"),
+        py::arg(okd) = "", "Crop a ``w`` x ``h`` window at a uniformly random position.");
+  c.def("image_random_crop_if", &T::image_random_crop_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("w"),
+        py::arg("h"), py::arg(okd) = "");
+  c.def("image_random_h_flip", &T::image_random_h_flip, nogil(), py::arg("key"), py::arg("prob"),
+        py::arg(okd) = "", "Mirror the image left-right with probability ``prob``.");
+  c.def("image_random_h_flip_if", &T::image_random_h_flip_if, nogil(), py::arg("cond"), py::arg("key"),
+        py::arg("prob"), py::arg(okd) = "");
+  c.def("image_resize", &T::image_resize, nogil(), py::arg("key"), py::arg("w"), py::arg("h"), py::arg(okd) = "",
+        "Resize the image to ``w`` x ``h`` (triangle filter; may change the aspect ratio).");
+  c.def("image_resize_if", &T::image_resize_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("w"),
+        py::arg("h"), py::arg(okd) = "");
+  c.def("image_resize_smallest_side", &T::image_resize_smallest_side, nogil(), py::arg("key"), py::arg("size"),
+        py::arg(okd) = "", "Resize so that the shorter side becomes ``size``, keeping the aspect ratio.");
+  c.def("image_resize_smallest_side_if", &T::image_resize_smallest_side_if, nogil(), py::arg("cond"),
+        py::arg("key"), py::arg("size"), py::arg(okd) = "");
+  c.def("image_rotate", &T::image_rotate, nogil(), py::arg("key"), py::arg("angle"), py::arg("crop") = false,
+        py::arg(okd) = "", py::arg("angle_key") = "",
+        "Rotate by ``angle`` degrees (nearest neighbour); ``crop`` keeps the input size. With ``angle_key`` "
+        "(an addition to mlx-data) the angle is read per sample from the float scalar at that key.");
+  c.def("image_rotate_if", &T::image_rotate_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("angle"),
+        py::arg("crop") = false, py::arg(okd) = "", py::arg("angle_key") = "");
+
+  auto key_transform = [](const T& ds, const std::string& key, py::function func, const std::string& okey) {
+    // the callable is kept in a holder that is released under the GIL
+    auto held = std::shared_ptr<py::function>(new py::function(std::move(func)), [](py::function* f) {
+      py::gil_scoped_acquire gil;
+      delete f;
+    });
+    auto fn = [held](const std::shared_ptr<const Array>& x) {
+      py::gil_scoped_acquire gil;
+      return to_array((*held)(to_numpy(x)));
+    };
+    py::gil_scoped_release nogil_scope;
+    return ds.key_transform(key, fn, okey);
+  };
+  c.def("key_transform", key_transform, py::arg("key"), py::arg("func"), py::arg(okd) = "",
+        "Apply the python function ``func`` to the array at ``key``.");
+  c.def("key_transform_if",
+        [key_transform](const T& ds, bool cond, const std::string& key, py::function func, const std::string& okey) {
+          return cond ? key_transform(ds, key, std::move(func), okey) : T(ds.node());
+        },
+        py::arg("cond"), py::arg("key"), py::arg("func"), py::arg(okd) = "");
+
+  auto sample_transform = [](const T& ds, py::function func) {
+    auto held = std::shared_ptr<py::function>(new py::function(std::move(func)), [](py::function* f) {
+      py::gil_scoped_acquire gil;
+      delete f;
+    });
+    auto fn = [held](const Sample& s) {
+      py::gil_scoped_acquire gil;
+      py::object r = (*held)(to_py_sample(s));
+      return to_sample(r.cast<py::dict>());
+    };
+    py::gil_scoped_release nogil_scope;
+    return ds.sample_transform(fn);
+  };
+  c.def("sample_transform", sample_transform, py::arg("func"),
+        "Apply the python function ``func`` to whole samples (dict in, dict out).");
+
+  auto key_cast = [](const T& ds, const std::string& key, const std::string& dtype, double scale,
+                     std::optional<std::vector<float>> mean, std::optional<std::vector<float>> std_,
+                     const std::string& okey) {
+    const gpu::CastSpec spec = make_cast(dtype, scale, mean, std_);
+    py::gil_scoped_release nogil_scope;
+    return ds.key_cast(key, spec, okey);
+  };
+  c.def("key_cast", key_cast, py::arg("key"), py::arg("dtype") = "float32", py::arg("scale") = 255.0,
+        py::arg("mean") = py::none(), py::arg("std") = py::none(), py::arg(okd) = "",
+        R"doc(
+        Cast the uint8 array at ``key`` to float32 on the GPU: ``x.astype("float32") / scale`` and,
+        with ``mean`` and ``std`` (one value per channel), ``(x / scale - mean) / std`` - the same
+        float32 arithmetic as the numpy expressions.  Placed directly after ``batch`` it is fused
+        into the batch kernel.  (Not part of mlx-data, where this is a python lambda.)
+        )doc");
+  c.def("key_cast_if",
+        [key_cast](const T& ds, bool cond, const std::string& key, const std::string& dtype, double scale,
+                   std::optional<std::vector<float>> mean, std::optional<std::vector<float>> std_,
+                   const std::string& okey) {
+          return cond ? key_cast(ds, key, dtype, scale, mean, std_, okey) : T(ds.node());
+        },
+        py::arg("cond"), py::arg("key"), py::arg("dtype") = "float32", py::arg("scale") = 255.0,
+        py::arg("mean") = py::none(), py::arg("std") = py::none(), py::arg(okd) = "");
+}
+
+struct BufferCursor {
+  Buffer buffer;
+  int64_t at = 0;
+};
+
+} // namespace
+
+PYBIND11_MODULE(_c, m) {
+  m.doc() = "B200-native image-transform-and-batch path with the mlx-data pipeline API";
+  using nogil = py::call_guard<py::gil_scoped_release>;
+  using MapD = std::unordered_map<std::string, double>;
+  using MapI = std::unordered_map<std::string, int>;
+
+  py::class_<BufferCursor>(m, "BufferIterator")
+      .def("__iter__", [](BufferCursor& c) -> BufferCursor& { return c; })
+      .def("__next__", [](BufferCursor& c) {
+        Sample s;
+        {
+          py::gil_scoped_release release;
+          if (c.at < c.buffer.size()) {
+            s = c.buffer.get(c.at++);
+          }
+        }
+        if (s.empty()) {
+          throw py::stop_iteration();
+        }
+        return to_py_sample(s);
+      });
+
+  py::class_<Buffer, std::unique_ptr<Buffer, ReleaseGilDeleter<Buffer>>> buffer(m, "Buffer");
+  buffer.def("__iter__", [](Buffer& b) { return BufferCursor{b, 0}; })
+      .def("size", &Buffer::size, nogil())
+      .def("__len__", &Buffer::size, nogil())
+      .def("__getitem__",
+           [](const Buffer& b, int64_t idx) {
+             Sample s;
+             {
+               py::gil_scoped_release release;
+               if (idx < 0) {
+                 idx += b.size();
+               }
+               s = b.get(idx);
+             }
+             return to_py_sample(s);
+           },
+           py::arg("idx"))
+      .def("__repr__",
+           [](const Buffer& b) {
+             std::ostringstream os;
+             os << "Buffer(size=" << b.size() << ")";
+             return os.str();
+           })
+      .def("batch",
+           [](const Buffer& b, py::object batch_size, const MapD& pad, const MapI& dim) {
+             if (py::isinstance<py::int_>(batch_size)) {
+               const int64_t n = batch_size.cast<int64_t>();
+               py::gil_scoped_release release;
+               return b.batch(n, pad, dim);
+             }
+             const auto sizes = batch_size.cast<std::vector<int64_t>>();
+             py::gil_scoped_release release;
+             return b.batch(sizes, pad, dim);
+           },
+           py::arg("batch_size"), py::arg("pad") = MapD(), py::arg("dim") = MapI(),
+           "Batch consecutive samples; ``batch_size`` is an int or a list of sizes. Arrays are padded "
+           "to the largest shape in the batch with ``pad[key]`` (default 0).")
+      .def("ordered_prefetch", &Buffer::ordered_prefetch, nogil(), py::arg("prefetch_size"), py::arg("num_thread"),
+           "Fetch samples in background threads, returning them in buffer order.")
+      .def("partition", &Buffer::partition, nogil(), py::arg("num_partitions"), py::arg("partition"))
+      .def("partition_if", &Buffer::partition_if, nogil(), py::arg("cond"), py::arg("num_partitions"),
+           py::arg("partition"))
+      .def("to_stream", &Buffer::to_stream, nogil());
+  bind_ops<Buffer>(buffer);
+
+  auto stream_next = [](Stream& s) {
+    Sample res;
+    {
+      py::gil_scoped_release release;
+      res = s.next();
+    }
+    return to_py_sample(res);
+  };
+  py::class_<Stream, std::unique_ptr<Stream, ReleaseGilDeleter<Stream>>> stream(m, "Stream");
+  stream.def("__iter__", [](Stream& s) { return s; })
+      .def("__next__",
+           [](Stream& s) {
+             Sample res;
+             {
+               py::gil_scoped_release release;
+               res = s.next();
+             }
+             if (res.empty()) {
+               throw py::stop_iteration();
+             }
+             return to_py_sample(res);
+           })
+      .def("__call__", stream_next)
+      .def("next", stream_next)
+      .def("__repr__", [](const Stream&) { return "Stream()"; })
+      .def("reset", &Stream::reset, nogil())
+      .def("batch", &Stream::batch, nogil(), py::arg("batch_size"), py::arg("pad") = MapD(), py::arg("dim") = MapI())
+      .def("partition", &Stream::partition, nogil(), py::arg("num_partitions"), py::arg("partition"))
+      .def("partition_if", &Stream::partition_if, nogil(), py::arg("cond"), py::arg("num_partitions"),
+           py::arg("partition"))
+      .def("prefetch", &Stream::prefetch, nogil(), py::arg("prefetch_size"), py::arg("num_threads"))
+      .def("prefetch_if", &Stream::prefetch_if, nogil(), py::arg("cond"), py::arg("prefetch_size"),
+           py::arg("num_threads"))
+      .def("to_buffer", &Stream::to_buffer, nogil());
+  bind_ops<Stream>(stream);
+
+  m.def("buffer_from_vector",
+        [](const std::vector<py::dict>& data) {
+          std::vector<Sample> samples;
+          samples.reserve(data.size());
+          for (auto& d : data) {
+            samples.push_back(to_sample(d));
+          }
+          py::gil_scoped_release release;
+          return buffer_from_vector(std::move(samples));
+        },
+        py::arg("data"), "Make a buffer from a list of dicts of arrays (numpy arrays are not copied).");
+
+  py::module core = m.def_submodule("core", "Process-wide state");
+  core.def("set_state", &core::set_state, py::arg("seed") = 1234,
+           "Seed the random generator used by the random ops.");
+  core.def("set_device", &gpu::Runtime::set_device, py::arg("device"),
+           "Choose the CUDA device; call before the first op runs.");
+  core.def("device", &gpu::Runtime::device);
+  core.def("pinned_empty",
+           [](const std::vector<int64_t>& shape, const std::string& dtype) {
+             const py::dtype dt(dtype);
+             auto arr = gpu::Runtime::get().pinned_array(dtype_to_type(dt), shape);
+             return to_numpy(arr);
+           },
+           py::arg("shape"), py::arg("dtype") = "uint8",
+           "A numpy array in page-locked host memory: samples stored in such arrays are copied to the "
+           "GPU asynchronously at full PCIe speed.");
+  core.def("stats", []() {
+    mlxd_stats s;
+    gpu::Runtime::get().check(mlxd_stats_get(gpu::Runtime::get().ctx(), &s));
+    py::dict d;
+    d["batches"] = s.batches;
+    d["samples"] = s.samples;
+    d["kernel_launches"] = s.kernel_launches;
+    d["h2d_bytes"] = s.h2d_bytes;
+    d["d2h_bytes"] = s.d2h_bytes;
+    d["device_bytes_reserved"] = s.device_bytes_reserved;
+    return d;
+  });
+}

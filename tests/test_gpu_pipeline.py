@@ -1,0 +1,136 @@
+"""GPU parity through the pipeline API: the same fluent chain on this package
+and on the reference (compiled from its own sources under oracle/_ref), same
+samples, same seed.  Exact for everything but resize, which is held to +-1
+uint8 LSB and to a bound on how often a difference may occur."""
+import importlib
+
+import numpy as np
+import pytest
+
+import refpipe
+
+pytestmark = pytest.mark.gpu
+
+RESIZE_MISMATCH_MAX = 1e-3
+
+
+def _wl():
+    return importlib.import_module("mlx_data_b200.workloads")
+
+
+def _check(got, want, has_resize, cast_scale):
+    assert len(got) == len(want)
+    for g, w in zip(got, want):
+        assert sorted(g.keys()) == sorted(w.keys())
+        for k in w:
+            a, b = np.asarray(g[k]), np.asarray(w[k])
+            assert a.shape == b.shape and a.dtype == b.dtype, (k, a.shape, b.shape, a.dtype, b.dtype)
+            if not has_resize or a.ndim < 4:
+                assert np.array_equal(a, b), k
+            else:
+                tol = 1.0 if a.dtype == np.uint8 else cast_scale * 1.0001
+                d = np.abs(a.astype(np.float64) - b.astype(np.float64))
+                assert d.max() <= tol, (k, d.max())
+                assert (a != b).mean() <= RESIZE_MISMATCH_MAX, (k, (a != b).mean())
+
+
+def _cast_scale(cast):
+    return 1.0 / 255 if len(cast) == 0 else 1.0 / 255 / min(cast[1])
+
+
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c5"])
+@pytest.mark.parametrize("mode", ["native_cast", "lambda_cast"])
+def test_config_through_stream_api(pkg, name, mode):
+    wl = _wl()
+    cfg = wl.CONFIGS[name]
+    samples = wl.make_samples(name, "small")
+    for i, s in enumerate(samples):
+        s["label"] = np.int64(i)
+    ops = wl.config_ops(name, "small", "gray_ops" if name == "c3" else "ops")
+    keys = {"image": cfg["cast"]}
+    if name == "c3":
+        keys["gray"] = ()
+    pad = {k: cfg["pad"] for k in keys}
+    batch = cfg["small"]["batch"]
+    want = refpipe.run_reference(samples, ops, batch, pad, keys, seed=0)
+    pkg.core.set_state(0)
+    got = [dict(b) for b in refpipe.build(pkg, samples, ops, batch, pad, keys,
+                                          native_cast=(mode == "native_cast"), product=True)]
+    _check(got, want, name != "c4", _cast_scale(cfg["cast"]))
+    assert [int(x) for b in got for x in b["label"]] == list(range(len(samples)))
+
+
+def test_buffer_api_and_ordered_prefetch(pkg):
+    wl = _wl()
+    cfg = wl.CONFIGS["c2"]
+    samples = wl.make_samples("c2", "small", n=24)
+    ops = wl.config_ops("c2", "small")
+    keys = {"image": cfg["cast"]}
+    want = refpipe.run_reference(samples, ops, 8, {"image": 0.0}, keys, seed=3)
+    pkg.core.set_state(3)
+    buf = refpipe.build(pkg, samples, ops, 8, {"image": 0.0}, keys, native_cast=True, buffer_mode=True)
+    assert len(buf) == 3
+    got = [dict(buf[i]) for i in range(3)]
+    _check(got, want, True, _cast_scale(cfg["cast"]))
+    # ordered prefetch keeps buffer order; shapes only (workers draw from their own generator copies)
+    stream = buf.ordered_prefetch(2, 2)
+    shapes = [b["image"].shape for b in stream]
+    assert shapes == [(8, 224, 224, 3)] * 3
+
+
+def test_prefetch_threads_deterministic_chain(pkg):
+    """A chain without random ops gives the same batches whatever the thread count."""
+    wl = _wl()
+    cfg = wl.CONFIGS["c1"]
+    samples = wl.make_samples("c1", "small", n=40)
+    for i, s in enumerate(samples):
+        s["label"] = np.int64(i)
+    ops = wl.config_ops("c1", "small")
+    want = refpipe.run_reference(samples, ops, 8, {"image": 0.0}, {"image": ()}, seed=0)
+    by_first = {int(b["label"][0]): b for b in want}
+    stream = refpipe.build(pkg, samples, ops, 8, {"image": 0.0}, {"image": ()}, native_cast=True, prefetch=(4, 4))
+    got = [dict(b) for b in stream]
+    assert len(got) == len(want)
+    assert sorted(int(b["label"][0]) for b in got) == sorted(by_first)
+    for b in got:
+        _check([b], [by_first[int(b["label"][0])]], True, 1.0 / 255)
+
+
+def test_unfused_ops_one_by_one(pkg):
+    """Ops applied without a batch node run as single launches and still match."""
+    rng = np.random.default_rng(8)
+    img = rng.integers(0, 256, (90, 130, 3), dtype=np.uint8)
+    dx = refpipe.reference_module()
+    if dx is None:
+        pytest.skip("needs oracle/_ref")
+    def chain(m):
+        m.core.set_state(11)
+        b = m.buffer_from_vector([{"image": img}])
+        b = (b.image_random_crop("image", 100, 80).image_rotate("image", 20.0, crop=False)
+             .image_resize("image", 64, 48).image_rotate("image", -10.0, crop=True)
+             .image_channel_reduction("image", "rec709", output_key="gray").image_random_h_flip("gray", 1.0))
+        return dict(b[0])
+    got, want = chain(pkg), chain(dx)
+    assert got["image"].shape == want["image"].shape
+    d = np.abs(got["image"].astype(int) - want["image"].astype(int))
+    assert d.max() <= 1
+    assert np.abs(got["gray"].astype(int) - want["gray"].astype(int)).max() <= 1
+
+
+def test_error_behaviour_matches(pkg):
+    img = np.zeros((10, 12, 3), np.uint8)
+    b = pkg.buffer_from_vector([{"image": img}])
+    with pytest.raises(RuntimeError, match="target image size larger"):
+        b.image_center_crop("image", 20, 5)[0]
+    with pytest.raises(RuntimeError, match="illegal target size"):
+        b.image_resize_smallest_side("image", 0)[0]
+    with pytest.raises(RuntimeError, match="expected a 3 channel"):
+        pkg.buffer_from_vector([{"image": np.zeros((4, 4, 1), np.uint8)}]).image_channel_reduction("image")[0]
+    with pytest.raises(RuntimeError, match="unable to find preset"):
+        b.image_channel_reduction("image", "nope")
+    with pytest.raises(RuntimeError, match="key <missing> expected"):
+        b.image_resize("missing", 4, 4)[0]
+    with pytest.raises(ValueError):
+        pkg.buffer_from_vector([{"image": np.zeros((4, 4, 3), np.float32)}]).image_resize("image", 2, 2)[0]
+    with pytest.raises(IndexError):
+        b[3]
