@@ -104,6 +104,10 @@ typedef struct mlxd_stats {
   uint64_t h2d_bytes;
   uint64_t d2h_bytes;
   uint64_t device_bytes_reserved; /* staging + output arenas currently held */
+  uint64_t kernel_ns;             /* summed device time of the timed launches (CUDA events around each kernel) */
+  uint64_t timed_launches;        /* launches included in kernel_ns; 0 unless timing is on */
+  uint64_t algo_src_bytes;        /* summed source footprints: the uint8 source rectangle each sample's chain can read */
+  uint64_t algo_dst_bytes;        /* summed batch tensor bytes written, padding included */
 } mlxd_stats;
 
 /* Context: one device, n_lanes independent lanes.  A lane owns a CUDA stream, a
@@ -121,6 +125,15 @@ MLXD_API const char* mlxd_last_error(void);
  * through the external-storage constructor (mlx/data/Array.h:28-31). */
 MLXD_API void* mlxd_pinned_alloc(size_t bytes);
 MLXD_API void mlxd_pinned_free(void* p);
+
+/* Device memory on the context's GPU, for sources and batches that stay in
+ * HBM (no counterpart in the reference, which is host-only).  NULL on failure. */
+MLXD_API void* mlxd_device_alloc(mlxd_ctx* ctx, size_t bytes);
+MLXD_API void mlxd_device_free(mlxd_ctx* ctx, void* p);
+
+/* Bracket every fused kernel with CUDA events on the stream it is launched on
+ * and add the elapsed device time to mlxd_stats.kernel_ns (off by default). */
+MLXD_API int mlxd_ctx_set_timing(mlxd_ctx* ctx, int on);
 
 /* Enqueue one fused batch on a lane and return: host sources are copied to the
  * device (only the rows the chain reads), one kernel writes every slot, and a

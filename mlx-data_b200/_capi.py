@@ -57,7 +57,8 @@ class BatchDesc(ctypes.Structure):
 
 class Stats(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint64) for n in (
-        "batches", "samples", "kernel_launches", "h2d_bytes", "d2h_bytes", "device_bytes_reserved")]
+        "batches", "samples", "kernel_launches", "h2d_bytes", "d2h_bytes", "device_bytes_reserved",
+        "kernel_ns", "timed_launches", "algo_src_bytes", "algo_dst_bytes")]
 
 
 # numpy mirror of SampleDesc so a whole batch of descriptors is one array
@@ -76,6 +77,7 @@ EXPORTS = [
     "mlxd_fused_batch", "mlxd_batch_wait", "mlxd_fused_batch_on_stream", "mlxd_image_resize",
     "mlxd_image_crop", "mlxd_image_hflip", "mlxd_image_affine", "mlxd_image_channel_reduction",
     "mlxd_batch_pad", "mlxd_cast_scale_normalise", "mlxd_stats_get",
+    "mlxd_device_alloc", "mlxd_device_free", "mlxd_ctx_set_timing",
 ]
 
 
@@ -119,6 +121,11 @@ def load():
                                    ctypes.POINTER(ctypes.c_int32), i32, i32, i32, i32, ctypes.c_double, vp]
     lib.mlxd_cast_scale_normalise.argtypes = [vp, vp, i64, i32, ctypes.c_float, vp, vp, vp]
     lib.mlxd_stats_get.argtypes = [vp, ctypes.POINTER(Stats)]
+    lib.mlxd_device_alloc.argtypes = [vp, ctypes.c_size_t]
+    lib.mlxd_device_alloc.restype = vp
+    lib.mlxd_device_free.argtypes = [vp, vp]
+    lib.mlxd_device_free.restype = None
+    lib.mlxd_ctx_set_timing.argtypes = [vp, i32]
     _lib = lib
     return lib
 
@@ -243,6 +250,9 @@ class Context:
         self._check(self.lib.mlxd_cast_scale_normalise(
             self.handle, x.ctypes.data, x.size // c, c, divisor, mp, sp, out.ctypes.data))
         return out
+
+    def set_timing(self, on=True):
+        self._check(self.lib.mlxd_ctx_set_timing(self.handle, 1 if on else 0))
 
     def stats(self):
         s = Stats()

@@ -21,6 +21,8 @@ void destroy_lane(Lane* l) {
     if (l->d_desc[s].ptr) cudaFree(l->d_desc[s].ptr);
     if (l->h_desc[s].ptr) cudaFreeHost(l->h_desc[s].ptr);
     if (l->desc_copied[s]) cudaEventDestroy(l->desc_copied[s]);
+    if (l->k_begin[s]) cudaEventDestroy(l->k_begin[s]);
+    if (l->k_end[s]) cudaEventDestroy(l->k_end[s]);
   }
   if (l->d_src.ptr) cudaFree(l->d_src.ptr);
   if (l->d_out.ptr) cudaFree(l->d_out.ptr);
@@ -39,6 +41,8 @@ int make_lane(Lane** out) {
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&l->done, cudaEventDisableTiming);
   for (int s = 0; s < kDescSlots && e == cudaSuccess; s++) {
     e = cudaEventCreateWithFlags(&l->desc_copied[s], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreate(&l->k_begin[s]);
+    if (e == cudaSuccess) e = cudaEventCreate(&l->k_end[s]);
   }
   if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&l->h_status), sizeof(int32_t), cudaHostAllocDefault);
   if (e != cudaSuccess) {
@@ -175,6 +179,36 @@ void mlxd_pinned_free(void* p) {
   }
 }
 
+void* mlxd_device_alloc(mlxd_ctx* ctx, size_t bytes) {
+  if (!ctx) {
+    fail(MLXD_ERR_INVALID, "mlxd_device_alloc: null context");
+    return nullptr;
+  }
+  void* p = nullptr;
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e == cudaSuccess) e = cudaMalloc(&p, bytes == 0 ? 1 : bytes);
+  if (e != cudaSuccess) {
+    fail_cuda(e, "cudaMalloc");
+    return nullptr;
+  }
+  return p;
+}
+
+void mlxd_device_free(mlxd_ctx* ctx, void* p) {
+  if (ctx && p) {
+    cudaSetDevice(ctx->device);
+    cudaFree(p);
+  }
+}
+
+int mlxd_ctx_set_timing(mlxd_ctx* ctx, int on) {
+  if (!ctx) {
+    return fail(MLXD_ERR_INVALID, "mlxd_ctx_set_timing: null context");
+  }
+  ctx->timing.store(on ? 1 : 0);
+  return MLXD_OK;
+}
+
 int mlxd_fused_batch(
     mlxd_ctx* ctx, int lane, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch) {
   if (!ctx || lane < 0 || lane >= ctx->n_user_lanes) {
@@ -219,15 +253,22 @@ int mlxd_fused_batch_on_stream(
   }
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)b.slot_h * b.slot_w * p.c_out * esize;
+  uint64_t algo_src = 0;
   for (int i = 0; i < n; i++) {
     dev[i].dst = static_cast<uint8_t*>(b.dst) + slot_bytes * i;
+    int32_t r0, r1, c0, c1;
+    needed_region(dev[i], 0, r0, r1, c0, c1);
+    algo_src += (uint64_t)(r1 - r0) * (uint64_t)(c1 - c0) * p.c_in;
   }
+  ctx->algo_src += algo_src;
+  ctx->algo_dst += slot_bytes * n;
   std::lock_guard<std::mutex> guard(ring.mu);
   const int slot = ring.next_slot;
   ring.next_slot = (slot + 1) % kDescSlots;
   // Here the slot's event is recorded after the kernel, so a finished wait
   // means neither the copy nor the kernel still needs the tables.
   MLXD_CUDA(cudaEventSynchronize(ring.desc_copied[slot]));
+  harvest_timing(ctx, ring, slot, true);
   rc = arena_reserve(ctx, ring.h_desc[slot], sizeof(DevSample) * n, true, nullptr);
   if (rc != MLXD_OK) {
     return rc;
@@ -240,7 +281,15 @@ int mlxd_fused_batch_on_stream(
   MLXD_CUDA(cudaMemcpyAsync(
       ring.d_desc[slot].ptr, ring.h_desc[slot].ptr, sizeof(DevSample) * n, cudaMemcpyHostToDevice, stream));
   p.samples = static_cast<const DevSample*>(ring.d_desc[slot].ptr);
+  const bool timed = ctx->timing.load() != 0;
+  if (timed) {
+    MLXD_CUDA(cudaEventRecord(ring.k_begin[slot], stream));
+  }
   MLXD_CUDA(launch_fused_batch(p, any_resize, stream));
+  if (timed) {
+    MLXD_CUDA(cudaEventRecord(ring.k_end[slot], stream));
+    ring.k_pending[slot] = true;
+  }
   MLXD_CUDA(cudaEventRecord(ring.desc_copied[slot], stream));
   ctx->batches += 1;
   ctx->samples += n;
@@ -384,6 +433,18 @@ int mlxd_stats_get(mlxd_ctx* ctx, mlxd_stats* out) {
   if (!ctx || !out) {
     return fail(MLXD_ERR_INVALID, "mlxd_stats_get: null argument");
   }
+  // launches on caller streams are harvested here, once they have finished
+  {
+    Lane& ring = *ctx->lanes[ctx->n_user_lanes + 1];
+    std::lock_guard<std::mutex> guard(ring.mu);
+    for (int s = 0; s < kDescSlots; s++) {
+      harvest_timing(ctx, ring, s, false);
+    }
+  }
+  out->algo_src_bytes = ctx->algo_src.load();
+  out->algo_dst_bytes = ctx->algo_dst.load();
+  out->kernel_ns = ctx->kernel_ns.load();
+  out->timed_launches = ctx->timed_launches.load();
   out->batches = ctx->batches.load();
   out->samples = ctx->samples.load();
   out->kernel_launches = ctx->launches.load();

@@ -193,24 +193,42 @@ int plan_samples(
   return MLXD_OK;
 }
 
-void source_rows(const DevSample& s, int32_t& r0, int32_t& r1) {
-  int64_t lo = 0, hi = s.pre_h;  // rows of the pre window
-  if (s.mode == kModeCopy) {
-    lo = s.post_y;
-    hi = (int64_t)s.post_y + s.post_h;
-  } else if (s.mode == kModeResize && s.pre_h != s.geom_h) {
-    const double ratio = (double)s.pre_h / (double)s.geom_h;
+// Source samples of an n_src -> n_dst axis that outputs [o_lo, o_hi) can read,
+// widened by `margin` on both sides and clipped to the axis.
+static void axis_span(int64_t n_src, int64_t n_dst, int64_t o_lo, int64_t o_hi, int margin, int64_t& lo, int64_t& hi) {
+  if (n_src == n_dst) {
+    lo = o_lo;
+    hi = o_hi;
+  } else {
+    const double ratio = (double)n_src / (double)n_dst;
     const double radius = ratio > 1.0 ? ratio : 1.0;
-    lo = (int64_t)std::floor((s.post_y + 0.5) * ratio - 0.5 - radius) - 2;
-    hi = (int64_t)std::ceil((s.post_y + s.post_h - 0.5) * ratio - 0.5 + radius) + 3;
-  } else if (s.mode == kModeResize) {
-    lo = s.post_y;
-    hi = (int64_t)s.post_y + s.post_h;
+    lo = (int64_t)std::floor((o_lo + 0.5) * ratio - 0.5 - radius) - margin;
+    hi = (int64_t)std::ceil((o_hi - 0.5) * ratio - 0.5 + radius) + 1 + margin;
   }
   lo = std::max<int64_t>(lo, 0);
-  hi = std::min<int64_t>(hi, s.pre_h);
-  r0 = (int32_t)(s.pre_y + lo);
-  r1 = (int32_t)(s.pre_y + hi);
+  hi = std::min<int64_t>(hi, n_src);
+}
+
+void needed_region(const DevSample& s, int margin, int32_t& r0, int32_t& r1, int32_t& c0, int32_t& c1) {
+  int64_t rlo = 0, rhi = s.pre_h, clo = 0, chi = s.pre_w;  // in pre-window coordinates
+  if (s.mode == kModeCopy) {
+    rlo = s.post_y;
+    rhi = (int64_t)s.post_y + s.post_h;
+    clo = s.post_x;
+    chi = (int64_t)s.post_x + s.post_w;
+  } else if (s.mode == kModeResize) {
+    axis_span(s.pre_h, s.geom_h, s.post_y, (int64_t)s.post_y + s.post_h, margin, rlo, rhi);
+    axis_span(s.pre_w, s.geom_w, s.post_x, (int64_t)s.post_x + s.post_w, margin, clo, chi);
+    if (s.pre_flip) {
+      const int64_t a = s.pre_w - chi, b = s.pre_w - clo;
+      clo = a;
+      chi = b;
+    }
+  }
+  r0 = (int32_t)(s.pre_y + rlo);
+  r1 = (int32_t)(s.pre_y + rhi);
+  c0 = (int32_t)(s.pre_x + clo);
+  c1 = (int32_t)(s.pre_x + chi);
 }
 
 int get_lut(mlxd_ctx* ctx, const mlxd_batch_desc* b, int c_out, const float** lut) {
@@ -333,6 +351,7 @@ int enqueue_on_lane(
   lane.next_slot = (slot + 1) % kDescSlots;
   // The pinned descriptor table of this slot may still be in flight.
   MLXD_CUDA(cudaEventSynchronize(lane.desc_copied[slot]));
+  harvest_timing(ctx, lane, slot, true);
   rc = arena_reserve(ctx, lane.h_desc[slot], sizeof(DevSample) * n, true, lane.stream);
   if (rc != MLXD_OK) {
     return rc;
@@ -344,32 +363,44 @@ int enqueue_on_lane(
 
   // Stage host sources: only the rows the chain reads, each block 256-byte aligned.
   struct Piece {
-    size_t offset, bytes;
+    size_t offset, row_bytes, rows, from_pitch;
     const uint8_t* from;
   };
   std::vector<Piece> pieces;
   size_t stage_bytes = 0;
+  uint64_t algo_src = 0;
+  for (int i = 0; i < n; i++) {
+    int32_t r0, r1, c0, c1;
+    needed_region(dev[i], 0, r0, r1, c0, c1);
+    algo_src += (uint64_t)(r1 - r0) * (uint64_t)(c1 - c0) * p.c_in;
+  }
+  ctx->algo_src += algo_src;
+  ctx->algo_dst += out_bytes;
   if (host_src) {
     pieces.resize(n);
     for (int i = 0; i < n; i++) {
-      int32_t r0, r1;
-      source_rows(dev[i], r0, r1);
-      const size_t pitch = (size_t)dev[i].src_w * p.c_in;
+      int32_t r0, r1, c0, c1;
+      needed_region(dev[i], 2, r0, r1, c0, c1);
+      // The staged block is an image of its own: rows [r0, r1), columns
+      // [c0, c1) of the source, tightly packed.
       pieces[i].offset = stage_bytes;
-      pieces[i].bytes = pitch * (size_t)(r1 - r0);
-      pieces[i].from = samples[i].src + pitch * (size_t)r0;
-      stage_bytes += (pieces[i].bytes + 255) & ~(size_t)255;
+      pieces[i].row_bytes = (size_t)(c1 - c0) * p.c_in;
+      pieces[i].rows = (size_t)(r1 - r0);
+      pieces[i].from_pitch = (size_t)dev[i].src_w * p.c_in;
+      pieces[i].from = samples[i].src + pieces[i].from_pitch * (size_t)r0 + (size_t)c0 * p.c_in;
+      stage_bytes += (pieces[i].row_bytes * pieces[i].rows + 255) & ~(size_t)255;
+      dev[i].src_w = c1 - c0;
+      dev[i].pre_x -= c0;
+      dev[i].r0_staged = r0;
     }
     rc = arena_reserve(ctx, lane.d_src, stage_bytes + 256, false, lane.stream);
     if (rc != MLXD_OK) {
       return rc;
     }
     for (int i = 0; i < n; i++) {
-      int32_t r0, r1;
-      source_rows(dev[i], r0, r1);
-      const size_t pitch = (size_t)dev[i].src_w * p.c_in;
-      // Base of a virtual full image whose rows [r0, r1) are the staged block.
-      dev[i].src = static_cast<const uint8_t*>(lane.d_src.ptr) + pieces[i].offset - pitch * (size_t)r0;
+      // Base of a virtual image whose rows from r0 on are the staged block.
+      dev[i].src = static_cast<const uint8_t*>(lane.d_src.ptr) + pieces[i].offset -
+          pieces[i].row_bytes * (size_t)dev[i].r0_staged;
     }
   }
   uint8_t* out_base = static_cast<uint8_t*>(batch->dst);
@@ -390,14 +421,28 @@ int enqueue_on_lane(
   MLXD_CUDA(cudaEventRecord(lane.desc_copied[slot], lane.stream));
   if (host_src) {
     for (int i = 0; i < n; i++) {
-      MLXD_CUDA(cudaMemcpyAsync(
-          static_cast<uint8_t*>(lane.d_src.ptr) + pieces[i].offset, pieces[i].from, pieces[i].bytes,
-          cudaMemcpyHostToDevice, lane.stream));
+      uint8_t* to = static_cast<uint8_t*>(lane.d_src.ptr) + pieces[i].offset;
+      if (pieces[i].row_bytes == pieces[i].from_pitch) {
+        MLXD_CUDA(cudaMemcpyAsync(
+            to, pieces[i].from, pieces[i].row_bytes * pieces[i].rows, cudaMemcpyHostToDevice, lane.stream));
+      } else {
+        MLXD_CUDA(cudaMemcpy2DAsync(
+            to, pieces[i].row_bytes, pieces[i].from, pieces[i].from_pitch, pieces[i].row_bytes, pieces[i].rows,
+            cudaMemcpyHostToDevice, lane.stream));
+      }
     }
     ctx->h2d += stage_bytes;
   }
   p.samples = static_cast<const DevSample*>(lane.d_desc[slot].ptr);
+  const bool timed = ctx->timing.load() != 0;
+  if (timed) {
+    MLXD_CUDA(cudaEventRecord(lane.k_begin[slot], lane.stream));
+  }
   MLXD_CUDA(launch_fused_batch(p, any_resize, lane.stream));
+  if (timed) {
+    MLXD_CUDA(cudaEventRecord(lane.k_end[slot], lane.stream));
+    lane.k_pending[slot] = true;
+  }
   if (host_dst) {
     MLXD_CUDA(cudaMemcpyAsync(batch->dst, lane.d_out.ptr, out_bytes, cudaMemcpyDeviceToHost, lane.stream));
     ctx->d2h += out_bytes;
@@ -408,6 +453,25 @@ int enqueue_on_lane(
   ctx->samples += n;
   ctx->launches += 1;
   return MLXD_OK;
+}
+
+void harvest_timing(mlxd_ctx* ctx, Lane& lane, int slot, bool block) {
+  if (!lane.k_pending[slot]) {
+    return;
+  }
+  if (block) {
+    if (cudaEventSynchronize(lane.k_end[slot]) != cudaSuccess) {
+      return;
+    }
+  } else if (cudaEventQuery(lane.k_end[slot]) != cudaSuccess) {
+    return;
+  }
+  float ms = 0.0f;
+  if (cudaEventElapsedTime(&ms, lane.k_begin[slot], lane.k_end[slot]) == cudaSuccess) {
+    ctx->kernel_ns += (uint64_t)((double)ms * 1e6);
+    ctx->timed_launches += 1;
+  }
+  lane.k_pending[slot] = false;
 }
 
 int wait_lane(mlxd_ctx* ctx, Lane& lane, int timeout_ms) {
@@ -429,6 +493,12 @@ int wait_lane(mlxd_ctx* ctx, Lane& lane, int timeout_ms) {
       }
     }
     std::this_thread::sleep_for(std::chrono::microseconds(20));
+  }
+  {
+    std::lock_guard<std::mutex> guard(lane.mu);
+    for (int s = 0; s < kDescSlots; s++) {
+      harvest_timing(ctx, lane, s, false);
+    }
   }
   if (*lane.h_status != 0) {
     return fail(MLXD_ERR_DEVICE, "kernel self-check failed (status " + std::to_string(*lane.h_status) + ")");

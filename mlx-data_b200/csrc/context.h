@@ -44,6 +44,9 @@ struct Lane {
   Arena d_desc[kDescSlots];           // DevSample tables
   Arena h_desc[kDescSlots];           // their pinned images
   cudaEvent_t desc_copied[kDescSlots] = {};
+  cudaEvent_t k_begin[kDescSlots] = {};   // timing events around the kernel of each slot
+  cudaEvent_t k_end[kDescSlots] = {};
+  bool k_pending[kDescSlots] = {};        // recorded, not yet added to the statistics
   int next_slot = 0;
   int32_t* h_status = nullptr;        // pinned copy of the device status word
   std::mutex mu;                      // one caller at a time per lane
@@ -67,6 +70,9 @@ struct mlxd_ctx {
   std::mutex lut_mu;
   std::map<mlxd::LutKey, float*> luts;
   std::atomic<uint64_t> batches{0}, samples{0}, launches{0}, h2d{0}, d2h{0}, reserved{0};
+  std::atomic<uint64_t> kernel_ns{0}, timed_launches{0};
+  std::atomic<uint64_t> algo_src{0}, algo_dst{0};
+  std::atomic<int> timing{0};
 };
 
 namespace mlxd {
@@ -83,8 +89,9 @@ int prepare_launch(mlxd_ctx* ctx, const mlxd_batch_desc* b, int n, LaunchParams&
 // Device cast table for a batch descriptor (cached per context).
 int get_lut(mlxd_ctx* ctx, const mlxd_batch_desc* b, int c_out, const float** lut);
 
-// Rows of a sample's source that its chain can read: [r0, r1).
-void source_rows(const DevSample& s, int32_t& r0, int32_t& r1);
+// Part of a sample's source that its chain can read: rows [r0, r1), columns
+// [c0, c1); `margin` widens a filter footprint by that many source samples.
+void needed_region(const DevSample& s, int margin, int32_t& r0, int32_t& r1, int32_t& c0, int32_t& c1);
 
 int arena_reserve(mlxd_ctx* ctx, Arena& a, size_t bytes, bool pinned, cudaStream_t stream_to_drain);
 
@@ -93,5 +100,10 @@ int enqueue_on_lane(
     const std::vector<void*>* per_sample_dst);
 
 int wait_lane(mlxd_ctx* ctx, Lane& lane, int timeout_ms);
+
+// Add the elapsed time of a finished, timed slot to the statistics.  With
+// `block` the call waits for the slot's kernel; otherwise unfinished slots
+// stay pending.
+void harvest_timing(mlxd_ctx* ctx, Lane& lane, int slot, bool block);
 
 } // namespace mlxd

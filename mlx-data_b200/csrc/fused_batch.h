@@ -37,7 +37,8 @@ struct __align__(16) DevSample {
   int32_t sub_h, sub_w;   // resize: geometric-output rows / columns filtered per pass
   int32_t cap_y, cap_x;   // resize: tap-count bound per axis
   float mx[6];
-  int32_t pad_[3];
+  int32_t r0_staged;      // host use: first source row held by the staged copy
+  int32_t pad_[2];
 };
 
 struct LaunchParams {

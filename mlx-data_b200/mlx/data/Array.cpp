@@ -92,10 +92,17 @@ void fill_as(void* p, int64_t n, double value) {
 
 } // namespace
 
-Array::Array(ArrayType type, const std::vector<int64_t>& shape, std::shared_ptr<void> data)
-    : type_(type), shape_(shape), data_(std::move(data)), itemsize_(array_type_size(type)) {
+Array::Array(ArrayType type, const std::vector<int64_t>& shape, std::shared_ptr<void> data, int device)
+    : type_(type), shape_(shape), data_(std::move(data)), itemsize_(array_type_size(type)), device_(device) {
   if (type_ == Any && size() != 0) {
     throw std::runtime_error("Array: cannot create a tensor of undetermined type");
+  }
+}
+
+void Array::require_host(const char* what) const {
+  if (device_ >= 0) {
+    throw std::runtime_error(std::string("Array: ") + what + " needs host memory, but the array lives on GPU " +
+                             std::to_string(device_));
   }
 }
 
@@ -115,7 +122,7 @@ Array::Array(ArrayType type, const std::vector<int64_t>& shape)
 }
 
 Array::Array(const std::shared_ptr<const Array>& src)
-    : type_(src->type_), shape_(src->shape_), data_(src->data_), itemsize_(src->itemsize_) {}
+    : type_(src->type_), shape_(src->shape_), data_(src->data_), itemsize_(src->itemsize_), device_(src->device_) {}
 
 Array::Array(const std::string& str) : Array(std::string_view(str)) {}
 
@@ -130,6 +137,7 @@ int64_t Array::size() const {
 }
 
 void Array::fill(double value) {
+  require_host("fill");
   const int64_t n = size();
   switch (type_) {
     case UInt8:
@@ -215,6 +223,7 @@ void Array::reshape(const std::vector<int64_t>& shape) {
 namespace array {
 
 std::shared_ptr<Array> clone(const std::shared_ptr<const Array>& arr) {
+  arr->require_host("clone");
   auto res = std::make_shared<Array>(arr->type(), arr->shape());
   if (arr->size() > 0) {
     std::memcpy(res->data(), arr->data(), static_cast<size_t>(arr->size() * arr->itemsize()));
@@ -241,6 +250,7 @@ std::shared_ptr<Array> pad(const std::shared_ptr<const Array>& arr, int dim, int
   if (lpad < 0 || rpad < 0) {
     throw std::runtime_error("Array: pad must be positive");
   }
+  arr->require_host("pad");
   if (dim < 0 || dim >= arr->ndim()) {
     throw std::runtime_error("Array: dim out of range");
   }
@@ -267,13 +277,15 @@ std::shared_ptr<Array> slice(const std::shared_ptr<const Array>& arr, int index0
   const int64_t step = count(shape) * arr->itemsize();
   // aliasing constructor: the view keeps the parent's storage alive
   std::shared_ptr<void> view(arr->storage(), static_cast<char*>(arr->data()) + step * index0);
-  return std::make_shared<Array>(arr->type(), shape, view);
+  return std::make_shared<Array>(arr->type(), shape, view, arr->device());
 }
 
 void copy(const std::shared_ptr<Array>& dst, const std::shared_ptr<const Array>& src) {
   if (dst->type() != src->type() || dst->shape() != src->shape()) {
     throw std::runtime_error("Array: copy expects arrays of the same type and shape");
   }
+  dst->require_host("copy");
+  src->require_host("copy");
   if (src->size() > 0) {
     std::memcpy(dst->data(), src->data(), static_cast<size_t>(src->size() * src->itemsize()));
   }
@@ -291,6 +303,7 @@ std::shared_ptr<Array> batch(const std::vector<std::shared_ptr<Array>>& arrs, do
     if (a->type() != type) {
       throw std::runtime_error("Array: unexpected different types of arrays in batch");
     }
+    a->require_host("batch");
     if (a->ndim() != nd) {
       throw std::runtime_error("BatchShape: batched arrays expected to have consistent shapes");
     }
@@ -329,6 +342,7 @@ std::shared_ptr<Array> batch(const std::vector<std::shared_ptr<Array>>& arrs, in
     if (a->type() != type) {
       throw std::runtime_error("Array: unexpected different types of arrays in batch");
     }
+    a->require_host("batch");
     if (a->ndim() != nd) {
       throw std::runtime_error("BatchShape: batched arrays expected to have consistent shapes");
     }
@@ -366,6 +380,7 @@ std::shared_ptr<Array> sub(const std::shared_ptr<const Array>& arr, std::vector<
       throw std::runtime_error("Array: sub: shape out of bound");
     }
   }
+  arr->require_host("sub");
   auto res = std::make_shared<Array>(arr->type(), shape);
   std::vector<int64_t> zero(shape.size(), 0);
   copy_block(

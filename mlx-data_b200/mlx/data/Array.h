@@ -31,8 +31,10 @@ class Array {
   Array(const std::string& str);
   Array(std::string_view str);
   Array(ArrayType type, const std::vector<int64_t>& shape);
-  // Adopt external storage; `data` keeps it alive and releases it.
-  Array(ArrayType type, const std::vector<int64_t>& shape, std::shared_ptr<void> data);
+  // Adopt external storage; `data` keeps it alive and releases it.  device >= 0
+  // marks storage that lives in that GPU's memory (an addition: mlx-data's
+  // arrays are host-only); host code must not dereference it.
+  Array(ArrayType type, const std::vector<int64_t>& shape, std::shared_ptr<void> data, int device = -1);
 
   template <class... Dims, class = std::enable_if_t<(std::is_integral_v<Dims> && ...) && (sizeof...(Dims) > 0)>>
   Array(ArrayType type, Dims... dims) : Array(type, std::vector<int64_t>{static_cast<int64_t>(dims)...}) {}
@@ -76,6 +78,10 @@ class Array {
   ArrayType type() const { return type_; }
   void* data() const { return data_.get(); }
   const std::shared_ptr<void>& storage() const { return data_; }
+  // -1: host memory; otherwise the CUDA device holding the storage.
+  int device() const { return device_; }
+  // Throws when the storage is on a GPU; host-side array helpers call this.
+  void require_host(const char* what) const;
 
   template <class T>
   T* data() const {
@@ -104,6 +110,7 @@ class Array {
   std::vector<int64_t> shape_;
   std::shared_ptr<void> data_;
   int64_t itemsize_ = 0;
+  int device_ = -1;
 };
 
 namespace array {

@@ -216,8 +216,8 @@ mlxd_ctx* Runtime::ctx() {
   std::lock_guard<std::mutex> g(mu_);
   if (!ctx_) {
     n_lanes_ = std::max(1, env_int("MLXD_LANES", 8));
-    const long long gib = env_int("MLXD_PINNED_POOL_GIB", 16);
-    pool_limit_ = static_cast<size_t>(gib) << 30;
+    pinned_pool_.limit = static_cast<size_t>(env_int("MLXD_PINNED_POOL_GIB", 16)) << 30;
+    device_pool_.limit = static_cast<size_t>(env_int("MLXD_DEVICE_POOL_GIB", 32)) << 30;
     mlxd_ctx* c = nullptr;
     const int rc = mlxd_ctx_create(device(), n_lanes_, &c);
     if (rc != MLXD_OK) {
@@ -242,51 +242,76 @@ int Runtime::lane() {
 
 Runtime::~Runtime() {}
 
-void* Runtime::pool_take(size_t bytes, size_t& held) {
+void Runtime::set_device_output(bool on) {
+  device_output_ = on;
+}
+
+void Runtime::set_stream(void* cuda_stream, bool enabled) {
+  ext_stream_ = cuda_stream;
+  use_ext_stream_ = enabled;
+}
+
+void* Runtime::pool_take(Pool& pool, size_t bytes, size_t& held) {
   std::lock_guard<std::mutex> g(mu_);
-  auto it = pool_.lower_bound(bytes);
+  auto it = pool.blocks.lower_bound(bytes);
   // reuse a block that is at most 25% larger than asked for
-  if (it != pool_.end() && it->first <= bytes + bytes / 4) {
+  if (it != pool.blocks.end() && it->first <= bytes + bytes / 4) {
     void* p = it->second;
     held = it->first;
-    pool_bytes_ -= it->first;
-    pool_.erase(it);
+    pool.bytes -= it->first;
+    pool.blocks.erase(it);
     return p;
   }
   return nullptr;
 }
 
-void Runtime::pool_give(void* p, size_t bytes) {
-  {
-    std::lock_guard<std::mutex> g(mu_);
-    if (pool_bytes_ + bytes <= pool_limit_) {
-      pool_.emplace(bytes, p);
-      pool_bytes_ += bytes;
-      return;
-    }
+bool Runtime::pool_give(Pool& pool, void* p, size_t bytes) {
+  std::lock_guard<std::mutex> g(mu_);
+  if (pool.bytes + bytes <= pool.limit) {
+    pool.blocks.emplace(bytes, p);
+    pool.bytes += bytes;
+    return true;
   }
-  mlxd_pinned_free(p);
+  return false;
 }
 
-std::shared_ptr<Array> Runtime::pinned_array(ArrayType type, const std::vector<int64_t>& shape) {
-  ctx();
+std::shared_ptr<Array> Runtime::pooled_array(ArrayType type, const std::vector<int64_t>& shape, bool on_device) {
+  mlxd_ctx* c = ctx();
   int64_t n = array_type_size(type);
   for (auto d : shape) {
     n *= d;
   }
   size_t bytes = static_cast<size_t>(std::max<int64_t>(n, 1));
   bytes = (bytes + 4095) & ~size_t(4095);
+  Pool& pool = on_device ? device_pool_ : pinned_pool_;
   size_t held = bytes;  // a recycled block goes back under the size it was allocated with
-  void* p = pool_take(bytes, held);
+  void* p = pool_take(pool, bytes, held);
   if (!p) {
-    p = mlxd_pinned_alloc(bytes);
+    p = on_device ? mlxd_device_alloc(c, bytes) : mlxd_pinned_alloc(bytes);
     if (!p) {
       throw std::runtime_error(std::string("mlx-data GPU path: ") + mlxd_last_error());
     }
   }
   Runtime* self = this;
-  std::shared_ptr<void> storage(p, [self, held](void* q) { self->pool_give(q, held); });
-  return std::make_shared<Array>(type, shape, storage);
+  std::shared_ptr<void> storage(p, [self, held, on_device, c](void* q) {
+    Pool& back = on_device ? self->device_pool_ : self->pinned_pool_;
+    if (!self->pool_give(back, q, held)) {
+      if (on_device) {
+        mlxd_device_free(c, q);
+      } else {
+        mlxd_pinned_free(q);
+      }
+    }
+  });
+  return std::make_shared<Array>(type, shape, storage, on_device ? device() : -1);
+}
+
+std::shared_ptr<Array> Runtime::pinned_array(ArrayType type, const std::vector<int64_t>& shape) {
+  return pooled_array(type, shape, false);
+}
+
+std::shared_ptr<Array> Runtime::device_array(ArrayType type, const std::vector<int64_t>& shape) {
+  return pooled_array(type, shape, true);
 }
 
 std::shared_ptr<Array> Runtime::batch(const std::vector<LazyImage>& images, double pad_value, const CastSpec* cast) {
@@ -296,6 +321,7 @@ std::shared_ptr<Array> Runtime::batch(const std::vector<LazyImage>& images, doub
   const int n = static_cast<int>(images.size());
   const LazyImage& first = images.front();
   int64_t max_h = 0, max_w = 0;
+  int on_device = 0;
   std::vector<mlxd_sample_desc> descs(images.size());
   for (int i = 0; i < n; i++) {
     const LazyImage& im = images[i];
@@ -305,10 +331,16 @@ std::shared_ptr<Array> Runtime::batch(const std::vector<LazyImage>& images, doub
     if (im.source_channels() != first.source_channels() || im.is_gray() != first.is_gray()) {
       throw std::runtime_error("BatchShape: batched arrays expected to have consistent shapes");
     }
+    on_device += im.source()->device() >= 0 ? 1 : 0;
     im.describe(descs[i]);
     max_h = std::max(max_h, im.height());
     max_w = std::max(max_w, im.width());
   }
+  if (on_device != 0 && on_device != n) {
+    throw std::runtime_error("batch: a batch cannot mix host and GPU-resident images");
+  }
+  const bool src_dev = on_device == n;
+  const bool dst_dev = device_output_;
   mlxd_batch_desc b;
   std::memset(&b, 0, sizeof(b));
   b.slot_h = to_i32(max_h, "height");
@@ -319,8 +351,8 @@ std::shared_ptr<Array> Runtime::batch(const std::vector<LazyImage>& images, doub
     first.gray_params(b.gray_m, b.gray_bias);
   }
   b.pad_value = pad_value;
-  b.src_mem = MLXD_MEM_HOST;
-  b.dst_mem = MLXD_MEM_HOST;
+  b.src_mem = src_dev ? MLXD_MEM_DEVICE : MLXD_MEM_HOST;
+  b.dst_mem = dst_dev ? MLXD_MEM_DEVICE : MLXD_MEM_HOST;
   b.divisor = 1.0f;
   ArrayType out_type = UInt8;
   if (cast) {
@@ -331,9 +363,15 @@ std::shared_ptr<Array> Runtime::batch(const std::vector<LazyImage>& images, doub
     std::memcpy(b.mean, cast->mean, sizeof(b.mean));
     std::memcpy(b.std_, cast->std_, sizeof(b.std_));
   }
-  auto out = pinned_array(out_type, {n, max_h, max_w, first.channels()});
+  const std::vector<int64_t> shape{n, max_h, max_w, first.channels()};
+  auto out = dst_dev ? device_array(out_type, shape) : pinned_array(out_type, shape);
   b.dst = out->data();
   mlxd_ctx* c = ctx();
+  if (src_dev && dst_dev && use_ext_stream_) {
+    // everything stays on the GPU: queue on the caller's stream and return
+    check(mlxd_fused_batch_on_stream(c, ext_stream_, descs.data(), n, &b));
+    return out;
+  }
   const int ln = lane();
   check(mlxd_fused_batch(c, ln, descs.data(), n, &b));
   check(mlxd_batch_wait(c, ln, -1));
@@ -347,6 +385,7 @@ std::shared_ptr<Array> Runtime::cast(const std::shared_ptr<const Array>& arr, co
   if (arr->ndim() < 1 || arr->shape(arr->ndim() - 1) < 1 || arr->shape(arr->ndim() - 1) > 4) {
     throw std::runtime_error("cast: the last dimension must hold 1 to 4 channels");
   }
+  arr->require_host("cast of a stand-alone array");
   const int c = static_cast<int>(arr->shape(arr->ndim() - 1));
   auto out = pinned_array(Float, arr->shape());
   if (arr->size() == 0) {

@@ -93,6 +93,17 @@ class Runtime {
 
   // Array whose storage is page-locked host memory from a recycling pool.
   std::shared_ptr<Array> pinned_array(ArrayType type, const std::vector<int64_t>& shape);
+  // Array whose storage is memory of the context's GPU, from a recycling pool.
+  std::shared_ptr<Array> device_array(ArrayType type, const std::vector<int64_t>& shape);
+
+  // Where batch() and cast() leave their results: host (default, what
+  // mlx-data does) or the GPU's memory, for consumers that train on that GPU.
+  void set_device_output(bool on);
+  bool device_output() const { return device_output_; }
+  // Launch on a caller-owned CUDA stream instead of the lanes.  Only used for
+  // work whose sources and result are all in GPU memory; such calls return
+  // without waiting and the result is ordered on that stream.
+  void set_stream(void* cuda_stream, bool enabled);
 
   // One fused launch: every image's program, batch + pad, optional cast.
   // Result is [N, max_h, max_w, C] uint8, or float32 when cast is given.
@@ -105,16 +116,24 @@ class Runtime {
 
  private:
   Runtime() = default;
-  void* pool_take(size_t bytes, size_t& held);
-  void pool_give(void* p, size_t bytes);
+  struct Pool {
+    std::multimap<size_t, void*> blocks;
+    size_t bytes = 0;
+    size_t limit = size_t(16) << 30;
+  };
+  void* pool_take(Pool& pool, size_t bytes, size_t& held);
+  bool pool_give(Pool& pool, void* p, size_t bytes);
+  std::shared_ptr<Array> pooled_array(ArrayType type, const std::vector<int64_t>& shape, bool on_device);
+  Pool device_pool_;
+  bool device_output_ = false;
+  void* ext_stream_ = nullptr;
+  bool use_ext_stream_ = false;
 
   std::mutex mu_;
   mlxd_ctx* ctx_ = nullptr;
   int n_lanes_ = 8;
   int next_lane_ = 0;
-  std::multimap<size_t, void*> pool_;
-  size_t pool_bytes_ = 0;
-  size_t pool_limit_ = size_t(16) << 30;
+  Pool pinned_pool_;
 };
 
 } // namespace gpu

@@ -65,7 +65,54 @@ std::shared_ptr<Array> wrap_numpy(py::array a) {
   return std::make_shared<Array>(type, shape, storage);
 }
 
+// A GPU-resident array as Python sees it: shape, dtype and the CUDA array
+// interface, which torch.as_tensor / cupy.asarray consume without a copy.
+struct PyDeviceArray {
+  std::shared_ptr<const Array> a;
+};
+
+const char* typestr_of(ArrayType t) {
+  switch (t) {
+    case Int8: return "|i1";
+    case UInt8: return "|u1";
+    case Int32: return "<i4";
+    case Int64: return "<i8";
+    case Float: return "<f4";
+    case Double: return "<f8";
+    default: throw std::runtime_error("internal error: unknown type");
+  }
+}
+
+// Object exposing __cuda_array_interface__ (a torch CUDA tensor, a cupy array)
+// -> Array that shares its GPU memory and keeps the object alive.
+std::shared_ptr<Array> wrap_cuda(py::handle obj) {
+  py::dict iface = obj.attr("__cuda_array_interface__").cast<py::dict>();
+  if (iface.contains("strides") && !iface["strides"].is_none()) {
+    throw std::runtime_error("[to_array] Contiguous GPU array expected -- call .contiguous() first");
+  }
+  const std::string typestr = iface["typestr"].cast<std::string>();
+  const py::dtype dt(typestr);
+  const ArrayType type = dtype_to_type(dt);
+  const auto shape = iface["shape"].cast<std::vector<int64_t>>();
+  const auto data = iface["data"].cast<py::tuple>();
+  void* ptr = reinterpret_cast<void*>(data[0].cast<uintptr_t>());
+  PyObject* keep = obj.inc_ref().ptr();
+  std::shared_ptr<void> storage(ptr, [keep](void*) {
+    py::gil_scoped_acquire gil;
+    Py_DECREF(keep);
+  });
+  return std::make_shared<Array>(type, shape, storage, gpu::Runtime::device());
+}
+
+py::object to_python(const std::shared_ptr<const Array>& a);
+
 std::shared_ptr<Array> to_array(py::handle obj) {
+  if (py::isinstance<PyDeviceArray>(obj)) {
+    return std::make_shared<Array>(obj.cast<PyDeviceArray&>().a);
+  }
+  if (py::hasattr(obj, "__cuda_array_interface__")) {
+    return wrap_cuda(obj);
+  }
   if (py::isinstance<py::array>(obj)) {
     return wrap_numpy(py::reinterpret_borrow<py::array>(obj));
   }
@@ -125,10 +172,17 @@ py::array to_numpy(const std::shared_ptr<const Array>& a) {
   return py::array(py::dtype(fmt), shape, strides, a->data(), owner);
 }
 
+py::object to_python(const std::shared_ptr<const Array>& a) {
+  if (a && a->device() >= 0) {
+    return py::cast(PyDeviceArray{a});
+  }
+  return to_numpy(a);
+}
+
 py::dict to_py_sample(const Sample& s) {
   py::dict d;
   for (auto& kv : s) {
-    d[py::str(kv.first)] = to_numpy(kv.second);
+    d[py::str(kv.first)] = to_python(kv.second);
   }
   return d;
 }
@@ -214,7 +268,7 @@ void bind_ops(PyClass& c) {
     });
     auto fn = [held](const std::shared_ptr<const Array>& x) {
       py::gil_scoped_acquire gil;
-      return to_array((*held)(to_numpy(x)));
+      return to_array((*held)(to_python(x)));
     };
     py::gil_scoped_release nogil_scope;
     return ds.key_transform(key, fn, okey);
@@ -280,6 +334,33 @@ PYBIND11_MODULE(_c, m) {
   using nogil = py::call_guard<py::gil_scoped_release>;
   using MapD = std::unordered_map<std::string, double>;
   using MapI = std::unordered_map<std::string, int>;
+
+  py::class_<PyDeviceArray>(m, "DeviceArray",
+                            "An array in GPU memory. Pass it to torch.as_tensor(x, device=\"cuda\") or "
+                            "cupy.asarray(x) to use it without a copy, or call numpy() to fetch it.")
+      .def_property_readonly("shape", [](const PyDeviceArray& d) { return py::tuple(py::cast(d.a->shape())); })
+      .def_property_readonly("dtype", [](const PyDeviceArray& d) { return py::dtype(typestr_of(d.a->type())); })
+      .def_property_readonly("device", [](const PyDeviceArray& d) { return d.a->device(); })
+      .def_property_readonly("nbytes", [](const PyDeviceArray& d) { return d.a->size() * d.a->itemsize(); })
+      .def_property_readonly("__cuda_array_interface__",
+                             [](const PyDeviceArray& d) {
+                               py::dict iface;
+                               iface["shape"] = py::tuple(py::cast(d.a->shape()));
+                               iface["typestr"] = typestr_of(d.a->type());
+                               iface["data"] = py::make_tuple(reinterpret_cast<uintptr_t>(d.a->data()), false);
+                               iface["version"] = 3;
+                               iface["strides"] = py::none();
+                               return iface;
+                             })
+      .def("__repr__", [](const PyDeviceArray& d) {
+        std::ostringstream os;
+        os << "DeviceArray(shape=(";
+        for (size_t i = 0; i < d.a->shape().size(); i++) {
+          os << (i ? ", " : "") << d.a->shape()[i];
+        }
+        os << "), device=" << d.a->device() << ")";
+        return os.str();
+      });
 
   py::class_<BufferCursor>(m, "BufferIterator")
       .def("__iter__", [](BufferCursor& c) -> BufferCursor& { return c; })
@@ -405,6 +486,18 @@ PYBIND11_MODULE(_c, m) {
            py::arg("shape"), py::arg("dtype") = "uint8",
            "A numpy array in page-locked host memory: samples stored in such arrays are copied to the "
            "GPU asynchronously at full PCIe speed.");
+  core.def("set_device_output", [](bool on) { gpu::Runtime::get().set_device_output(on); }, py::arg("on"),
+           "Leave batches in GPU memory (returned as DeviceArray) instead of copying them to the host.");
+  core.def("set_stream",
+           [](uintptr_t stream, bool enabled) {
+             gpu::Runtime::get().set_stream(reinterpret_cast<void*>(stream), enabled);
+           },
+           py::arg("cuda_stream"), py::arg("enabled") = true,
+           "Queue GPU-to-GPU work (GPU-resident samples and device output) on this CUDA stream handle "
+           "without waiting for it; pass enabled=False to go back to the internal lanes.");
+  core.def("set_timing",
+           [](bool on) { gpu::Runtime::get().check(mlxd_ctx_set_timing(gpu::Runtime::get().ctx(), on ? 1 : 0)); },
+           py::arg("on"), "Time every fused kernel with CUDA events; totals appear in stats().");
   core.def("stats", []() {
     mlxd_stats s;
     gpu::Runtime::get().check(mlxd_stats_get(gpu::Runtime::get().ctx(), &s));
@@ -415,6 +508,10 @@ PYBIND11_MODULE(_c, m) {
     d["h2d_bytes"] = s.h2d_bytes;
     d["d2h_bytes"] = s.d2h_bytes;
     d["device_bytes_reserved"] = s.device_bytes_reserved;
+    d["kernel_ns"] = s.kernel_ns;
+    d["timed_launches"] = s.timed_launches;
+    d["algo_src_bytes"] = s.algo_src_bytes;
+    d["algo_dst_bytes"] = s.algo_dst_bytes;
     return d;
   });
 }
