@@ -251,6 +251,8 @@ def main():
     ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--pool", type=int, default=0, help="distinct source images per GPU (0: workload default)")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="images per step per GPU (0: the workload's batch size; smaller values are for profiling)")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end leg (0: min(steps, 6))")
     ap.add_argument("--cpu-images", type=int, default=0, help="images per CPU-baseline run (0: workload default)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -276,7 +278,7 @@ def main():
     dx = load_package()
     dx.core.set_device(local)
 
-    batch = cfg["full"]["batch"]
+    batch = args.batch or cfg["full"]["batch"]
     K, W = args.steps, max(args.warmup, 3)
     pool_n = args.pool or {"c1": 2048, "c2": 4096, "c3": 2048, "c4": 4096, "c5": 512}[name]
     shapes = pool_shapes(wl, name, pool_n)
@@ -317,7 +319,7 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     ms_total = ev0.elapsed_time(ev1)
     st1 = dx.core.stats()
-    out_shape = tuple(out.shape)
+    out_shape = tuple(out["image"].shape)
     t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -335,7 +335,7 @@ PYBIND11_MODULE(_c, m) {
   using MapD = std::unordered_map<std::string, double>;
   using MapI = std::unordered_map<std::string, int>;
 
-  py::class_<PyDeviceArray>(m, "DeviceArray",
+  py::class_<PyDeviceArray>(m, "DeviceArray", py::module_local(),
                             "An array in GPU memory. Pass it to torch.as_tensor(x, device=\"cuda\") or "
                             "cupy.asarray(x) to use it without a copy, or call numpy() to fetch it.")
       .def_property_readonly("shape", [](const PyDeviceArray& d) { return py::tuple(py::cast(d.a->shape())); })
@@ -362,7 +362,7 @@ PYBIND11_MODULE(_c, m) {
         return os.str();
       });
 
-  py::class_<BufferCursor>(m, "BufferIterator")
+  py::class_<BufferCursor>(m, "BufferIterator", py::module_local())
       .def("__iter__", [](BufferCursor& c) -> BufferCursor& { return c; })
       .def("__next__", [](BufferCursor& c) {
         Sample s;
@@ -378,7 +378,7 @@ PYBIND11_MODULE(_c, m) {
         return to_py_sample(s);
       });
 
-  py::class_<Buffer, std::unique_ptr<Buffer, ReleaseGilDeleter<Buffer>>> buffer(m, "Buffer");
+  py::class_<Buffer, std::unique_ptr<Buffer, ReleaseGilDeleter<Buffer>>> buffer(m, "Buffer", py::module_local());
   buffer.def("__iter__", [](Buffer& b) { return BufferCursor{b, 0}; })
       .def("size", &Buffer::size, nogil())
       .def("__len__", &Buffer::size, nogil())
@@ -431,7 +431,7 @@ PYBIND11_MODULE(_c, m) {
     }
     return to_py_sample(res);
   };
-  py::class_<Stream, std::unique_ptr<Stream, ReleaseGilDeleter<Stream>>> stream(m, "Stream");
+  py::class_<Stream, std::unique_ptr<Stream, ReleaseGilDeleter<Stream>>> stream(m, "Stream", py::module_local());
   stream.def("__iter__", [](Stream& s) { return s; })
       .def("__next__",
            [](Stream& s) {
