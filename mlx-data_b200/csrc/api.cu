@@ -239,7 +239,7 @@ int mlxd_fused_batch_on_stream(
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   // validate + plan
   std::vector<DevSample> dev;
-  bool any_resize = false;
+  PassNeed need;
   mlxd_batch_desc b = *batch;
   Lane& ring = *ctx->lanes[ctx->n_user_lanes + 1];
   LaunchParams p;
@@ -247,10 +247,13 @@ int mlxd_fused_batch_on_stream(
   if (rc != MLXD_OK) {
     return rc;
   }
-  rc = plan_samples(samples, n, &b, dev, any_resize);
+  rc = plan_samples(samples, n, &b, dev, need);
   if (rc != MLXD_OK) {
     return rc;
   }
+  p.src_tile_bytes = need.src_bytes;
+  p.mid_float4s = need.mid_float4s;
+  p.weight_floats = need.weight_floats;
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)b.slot_h * b.slot_w * p.c_out * esize;
   uint64_t algo_src = 0;
@@ -285,7 +288,7 @@ int mlxd_fused_batch_on_stream(
   if (timed) {
     MLXD_CUDA(cudaEventRecord(ring.k_begin[slot], stream));
   }
-  MLXD_CUDA(launch_fused_batch(p, any_resize, stream));
+  MLXD_CUDA(launch_fused_batch(p, stream));
   if (timed) {
     MLXD_CUDA(cudaEventRecord(ring.k_end[slot], stream));
     ring.k_pending[slot] = true;

@@ -99,21 +99,21 @@ static int check_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc*
   return MLXD_OK;
 }
 
-static int plan_resize(DevSample& s, int C, int i) {
+static int plan_resize(DevSample& s, int C, int i, PassNeed& need) {
   int sub_h = kTileH, sub_w = kTileW;
   for (;;) {
-    AxisPlan ay = plan_axis(s.pre_h, s.geom_h, sub_h);
-    AxisPlan ax = plan_axis(s.pre_w, s.geom_w, sub_w);
-    const int64_t ext_y = std::min<int64_t>(ay.extent, s.pre_h);
-    const int64_t ext_x = std::min<int64_t>(ax.extent, s.pre_w);
-    const int64_t pitch = (ext_x * C + 3) & ~(int64_t)3;
-    const bool ok = ext_y * pitch <= kSrcTileBytes && (int64_t)sub_h * pitch <= kMidFloats &&
-        (int64_t)sub_h * ay.cap + (int64_t)sub_w * ax.cap <= kWeightFloats;
-    if (ok) {
+    const AxisPlan ay = plan_axis(s.pre_h, s.geom_h, sub_h);
+    const AxisPlan ax = plan_axis(s.pre_w, s.geom_w, sub_w);
+    bool fits = false;
+    const PassNeed n = plan_pass(ay, ax, sub_h, sub_w, s.pre_h, s.pre_w, C, fits);
+    if (fits) {
       s.sub_h = sub_h;
       s.sub_w = sub_w;
       s.cap_y = ay.cap;
       s.cap_x = ax.cap;
+      need.src_bytes = std::max(need.src_bytes, n.src_bytes);
+      need.mid_float4s = std::max(need.mid_float4s, n.mid_float4s);
+      need.weight_floats = std::max(need.weight_floats, n.weight_floats);
       return MLXD_OK;
     }
     if (sub_h > 4) {
@@ -134,8 +134,8 @@ static int plan_resize(DevSample& s, int C, int i) {
 
 int plan_samples(
     const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b,
-    std::vector<DevSample>& out, bool& any_resize) {
-  any_resize = false;
+    std::vector<DevSample>& out, PassNeed& need) {
+  need = PassNeed{0, 0, 0};
   out.resize(n);
   for (int i = 0; i < n; i++) {
     const mlxd_sample_desc& d = samples[i];
@@ -171,11 +171,10 @@ int plan_samples(
         s.mode = kModeCopy;  // identity on both axes
       } else {
         s.mode = kModeResize;
-        rc = plan_resize(s, b->channels, i);
+        rc = plan_resize(s, b->channels, i, need);
         if (rc != MLXD_OK) {
           return rc;
         }
-        any_resize = true;
       }
     } else if (d.geom == MLXD_GEOM_AFFINE) {
       s.mode = kModeAffine;
@@ -332,11 +331,14 @@ int enqueue_on_lane(
     return rc;
   }
   std::vector<DevSample> dev;
-  bool any_resize = false;
-  rc = plan_samples(samples, n, batch, dev, any_resize);
+  PassNeed need;
+  rc = plan_samples(samples, n, batch, dev, need);
   if (rc != MLXD_OK) {
     return rc;
   }
+  p.src_tile_bytes = need.src_bytes;
+  p.mid_float4s = need.mid_float4s;
+  p.weight_floats = need.weight_floats;
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)batch->slot_h * batch->slot_w * p.c_out * esize;
   const size_t out_bytes = slot_bytes * n;
@@ -438,7 +440,7 @@ int enqueue_on_lane(
   if (timed) {
     MLXD_CUDA(cudaEventRecord(lane.k_begin[slot], lane.stream));
   }
-  MLXD_CUDA(launch_fused_batch(p, any_resize, lane.stream));
+  MLXD_CUDA(launch_fused_batch(p, lane.stream));
   if (timed) {
     MLXD_CUDA(cudaEventRecord(lane.k_end[slot], lane.stream));
     lane.k_pending[slot] = true;

@@ -81,7 +81,7 @@ namespace mlxd {
 // filled by the caller).  Returns MLXD_OK or an error with the message set.
 int plan_samples(
     const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b,
-    std::vector<DevSample>& out, bool& any_resize);
+    std::vector<DevSample>& out, PassNeed& need);
 
 // Launch-wide parameters (cast table included) from a batch descriptor.
 int prepare_launch(mlxd_ctx* ctx, const mlxd_batch_desc* b, int n, LaunchParams& p);

@@ -65,6 +65,14 @@ __device__ __forceinline__ int quantise(float acc) {
   return r < 0.0f ? 0 : (r > 255.0f ? 255 : (int)r);
 }
 
+} // namespace
+} // namespace mlxd
+
+#include "resize_fast.cuh"
+
+namespace mlxd {
+namespace {
+
 struct SmemLayout {
   float* lut;
   uint8_t* outq;
@@ -72,16 +80,22 @@ struct SmemLayout {
   int* vcount;
   int* hfirst;
   int* hcount;
+  int2* rowinfo;
+  uint64_t* bar;
   float* wts;
   float* mid;
   uint8_t* srct;
 };
 
-__device__ __forceinline__ SmemLayout carve(unsigned char* base, int c_out, bool resize) {
+__host__ __device__ inline size_t align16(size_t v) {
+  return (v + 15) & ~(size_t)15;
+}
+
+__device__ __forceinline__ SmemLayout carve(unsigned char* base, const LaunchParams& p) {
   SmemLayout l;
   size_t off = 0;
   l.lut = reinterpret_cast<float*>(base + off);
-  off += (size_t)c_out * 256 * sizeof(float);
+  off += (size_t)p.c_out * 256 * sizeof(float);
   l.outq = base + off;
   off += kTileH * kTileW * 4;
   l.vfirst = reinterpret_cast<int*>(base + off);
@@ -92,22 +106,71 @@ __device__ __forceinline__ SmemLayout carve(unsigned char* base, int c_out, bool
   off += kTileW * sizeof(int);
   l.hcount = reinterpret_cast<int*>(base + off);
   off += kTileW * sizeof(int);
+  l.rowinfo = reinterpret_cast<int2*>(base + off);
+  off += kMaxStagedRows * sizeof(int2);
+  l.bar = reinterpret_cast<uint64_t*>(base + off);
+  off += 16;
   l.wts = reinterpret_cast<float*>(base + off);
-  l.mid = nullptr;
-  l.srct = nullptr;
-  if (resize) {
-    off += kWeightFloats * sizeof(float);
-    l.mid = reinterpret_cast<float*>(base + off);
-    off += kMidFloats * sizeof(float);
-    l.srct = base + off;
-  }
+  off = align16(off + (size_t)p.weight_floats * sizeof(float));
+  l.mid = reinterpret_cast<float*>(base + off);
+  off = align16(off + (size_t)p.mid_float4s * 16);
+  l.srct = base + off;
   return l;
 }
 
-// Filter the geometric-output rectangle [gy_lo, gy_hi) x [gx_lo, gx_hi) of a
-// resize sample into outq, sub_h x sub_w outputs per pass: stage the source
-// footprint in shared memory, filter vertically into float rows, filter
-// horizontally, quantise.
+// Pad value (already cast) into the rectangle [ya, yb) x [xa, xb) of a slot,
+// 16-byte stores wherever the row segment allows.
+__device__ void fill_rect_f32(
+    float* base, int slot_w, int co, int ya, int yb, int xa, int xb, const float* padf) {
+  if (ya >= yb || xa >= xb) {
+    return;
+  }
+  const int L = (xb - xa) * co;
+  const int Q = ((L + 3) >> 2) + 2;
+  const int ny = yb - ya;
+  for (int i = threadIdx.x; i < ny * Q; i += kThreads) {
+    const int ry = i / Q;
+    const int q = i - ry * Q;
+    float* rowp = base + ((size_t)(ya + ry) * slot_w + xa) * co;
+    const int mis = (int)((reinterpret_cast<uintptr_t>(rowp) >> 2) & 3);
+    int head = (4 - mis) & 3;
+    head = head > L ? L : head;
+    const int nvec = (L - head) >> 2;
+    if (q == 0) {
+      for (int j = 0; j < head; j++) {
+        rowp[j] = padf[j % co];
+      }
+    } else if (q <= nvec) {
+      const int j = head + 4 * (q - 1);
+      const int m = j % co;
+      *reinterpret_cast<float4*>(rowp + j) =
+          make_float4(padf[m], padf[(m + 1) % co], padf[(m + 2) % co], padf[(m + 3) % co]);
+    } else if (q == nvec + 1) {
+      for (int j = head + 4 * nvec; j < L; j++) {
+        rowp[j] = padf[j % co];
+      }
+    }
+  }
+}
+
+__device__ void fill_rect_u8(
+    uint8_t* base, int slot_w, int co, int ya, int yb, int xa, int xb, int pad_px) {
+  if (ya >= yb || xa >= xb) {
+    return;
+  }
+  const int L = (xb - xa) * co;
+  const int ny = yb - ya;
+  for (int i = threadIdx.x; i < ny * L; i += kThreads) {
+    const int ry = i / L;
+    const int j = i - ry * L;
+    base[((size_t)(ya + ry) * slot_w + xa) * co + j] = (uint8_t)pad_px;
+  }
+}
+
+// Generic resize of the geometric-output rectangle [gy_lo, gy_hi) x
+// [gx_lo, gx_hi) into outq (uint8), sub_h x sub_w outputs per pass.  Handles
+// every channel count, mirrored sources and uint8 destinations; the common
+// float32 case runs fast::resize_pass instead.
 __device__ void resize_region(
     const DevSample& s, const LaunchParams& p, const SmemLayout& sm,
     int y0, int x0, int gy_lo, int gy_hi, int gx_lo, int gx_hi) {
@@ -136,7 +199,7 @@ __device__ void resize_region(
       const int wbytes = (chi - clo + 1) * C;
       const int pitch = (wbytes + 3) & ~3;
       const int nwords = pitch >> 2;
-      if (rows * pitch > kSrcTileBytes || nr * pitch > kMidFloats) {
+      if (rows * pitch > p.src_tile_bytes || nr * pitch > p.mid_float4s * 4) {
         // The host planner sizes sub_h, sub_w so this cannot happen; record it
         // instead of overrunning shared memory.
         if (tid == 0) {
@@ -221,9 +284,37 @@ __device__ void resize_region(
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 2) fused_batch_kernel(const LaunchParams p, const int resize_smem) {
+template <int C>
+__device__ void resize_tile_fast(
+    const DevSample& s, const LaunchParams& p, const SmemLayout& sm,
+    int gy_lo, int gy_hi, int gx_lo, int gx_hi) {
+  fast::Layout fl;
+  fl.lut = sm.lut;
+  fl.vfirst = sm.vfirst;
+  fl.vcount = sm.vcount;
+  fl.hfirst = sm.hfirst;
+  fl.hcount = sm.hcount;
+  fl.rowinfo = sm.rowinfo;
+  fl.wts = sm.wts;
+  fl.mid = reinterpret_cast<float4*>(sm.mid);
+  fl.srct = sm.srct;
+  fl.bar = sm.bar;
+  if (threadIdx.x == 0) {
+    fast::mbar_init(sm.bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  unsigned parity = 0;
+  for (int by = gy_lo; by < gy_hi; by += s.sub_h) {
+    for (int bx = gx_lo; bx < gx_hi; bx += s.sub_w) {
+      fast::resize_pass<C>(s, p, fl, parity, by, bx, min(s.sub_h, gy_hi - by), min(s.sub_w, gx_hi - bx));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 3) fused_batch_kernel(const LaunchParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const SmemLayout sm = carve(smem_raw, p.c_out, resize_smem != 0);
+  const SmemLayout sm = carve(smem_raw, p);
   const int tid = threadIdx.x;
 
   unsigned t = blockIdx.x;
@@ -246,84 +337,111 @@ __global__ void __launch_bounds__(kThreads, 2) fused_batch_kernel(const LaunchPa
   const int vx1 = min(x1, s.post_w);
   const bool has_valid = (y0 < vy1) && (x0 < vx1);
   const int C = p.c_in;
+  const int co = p.c_out;
 
-  if (has_valid) {
-    if (p.out_f32) {
-      for (int i = tid; i < p.c_out * 256; i += kThreads) {
-        sm.lut[i] = __ldg(p.lut + i);
-      }
+  float padf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (p.out_f32) {
+    for (int c = 0; c < co; c++) {
+      padf[c] = __ldg(p.lut + c * 256 + p.pad_px);
     }
-    const int nvy = vy1 - y0;
-    const int nvx = vx1 - x0;
-    if (s.mode == kModeResize) {
-      int gx_lo, gx_hi;
-      if (!s.post_flip) {
-        gx_lo = s.post_x + x0;
-        gx_hi = s.post_x + vx1;
+  }
+  if (!has_valid) {
+    if (p.out_f32) {
+      fill_rect_f32(reinterpret_cast<float*>(s.dst), s.slot_w, co, y0, y1, x0, x1, padf);
+    } else {
+      fill_rect_u8(reinterpret_cast<uint8_t*>(s.dst), s.slot_w, co, y0, y1, x0, x1, p.pad_px);
+    }
+    return;
+  }
+
+  if (p.out_f32) {
+    for (int i = tid; i < co * 256; i += kThreads) {
+      sm.lut[i] = __ldg(p.lut + i);
+    }
+  }
+  const int nvy = vy1 - y0;
+  const int nvx = vx1 - x0;
+  if (s.mode == kModeResize) {
+    int gx_lo, gx_hi;
+    if (!s.post_flip) {
+      gx_lo = s.post_x + x0;
+      gx_hi = s.post_x + vx1;
+    } else {
+      gx_lo = s.post_x + s.post_w - vx1;
+      gx_hi = s.post_x + s.post_w - x0;
+    }
+    const bool fast_ok = p.out_f32 && !p.gray && !s.pre_flip && (C == 1 || C == 3 || C == 4);
+    if (fast_ok) {
+      if (C == 3) {
+        resize_tile_fast<3>(s, p, sm, s.post_y + y0, s.post_y + vy1, gx_lo, gx_hi);
+      } else if (C == 1) {
+        resize_tile_fast<1>(s, p, sm, s.post_y + y0, s.post_y + vy1, gx_lo, gx_hi);
       } else {
-        gx_lo = s.post_x + s.post_w - vx1;
-        gx_hi = s.post_x + s.post_w - x0;
+        resize_tile_fast<4>(s, p, sm, s.post_y + y0, s.post_y + vy1, gx_lo, gx_hi);
       }
-      resize_region(s, p, sm, y0, x0, s.post_y + y0, s.post_y + vy1, gx_lo, gx_hi);
-    } else if (s.mode == kModeAffine) {
-      // Nearest-neighbour warp.  The coordinate is built from float products
-      // and float sums, then two double additions, then truncation toward
-      // zero - the evaluation order of the reference expression - and no
-      // multiply-add is contracted.
-      const float twh = (float)((double)s.geom_w / 2.0);
-      const float thh = (float)((double)s.geom_h / 2.0);
-      const float wh = (float)((double)s.pre_w / 2.0);
-      const float hh = (float)((double)s.pre_h / 2.0);
-      for (int i = tid; i < nvy * nvx; i += kThreads) {
-        const int ry = i / nvx;
-        const int rx = i - ry * nvx;
-        const int px = s.post_flip ? (s.post_w - 1 - (x0 + rx)) : (x0 + rx);
-        const float dxf = __fsub_rn((float)(long long)(s.post_x + px), twh);
-        const float dyf = __fsub_rn((float)(long long)(s.post_y + y0 + ry), thh);
-        const float fx = __fadd_rn(__fadd_rn(__fmul_rn(s.mx[0], dxf), __fmul_rn(s.mx[1], dyf)), s.mx[2]);
-        const float fy = __fadd_rn(__fadd_rn(__fmul_rn(s.mx[3], dxf), __fmul_rn(s.mx[4], dyf)), s.mx[5]);
-        const long long ax = (long long)__dadd_rn(__dadd_rn((double)fx, 0.5), (double)wh);
-        const long long ay = (long long)__dadd_rn(__dadd_rn((double)fy, 0.5), (double)hh);
-        uint8_t* q = sm.outq + (ry * kTileW + rx) * C;
-        if (ax < 0 || ay < 0 || ax >= s.pre_w || ay >= s.pre_h) {
-          for (int ch = 0; ch < C; ch++) {
-            q[ch] = 0;
-          }
-        } else {
-          const int sx = s.pre_x + (s.pre_flip ? (s.pre_w - 1 - (int)ax) : (int)ax);
-          const int sy = s.pre_y + (int)ay;
-          const uint8_t* g = s.src + ((size_t)sy * s.src_w + sx) * C;
-          for (int ch = 0; ch < C; ch++) {
-            q[ch] = __ldg(g + ch);
-          }
+      // pad the part of the tile outside the post window
+      fill_rect_f32(reinterpret_cast<float*>(s.dst), s.slot_w, co, vy1, y1, x0, x1, padf);
+      fill_rect_f32(reinterpret_cast<float*>(s.dst), s.slot_w, co, y0, vy1, vx1, x1, padf);
+      return;
+    }
+    resize_region(s, p, sm, y0, x0, s.post_y + y0, s.post_y + vy1, gx_lo, gx_hi);
+  } else if (s.mode == kModeAffine) {
+    // Nearest-neighbour warp.  The coordinate is built from float products
+    // and float sums, then two double additions, then truncation toward
+    // zero - the evaluation order of the reference expression - and no
+    // multiply-add is contracted.
+    const float twh = (float)((double)s.geom_w / 2.0);
+    const float thh = (float)((double)s.geom_h / 2.0);
+    const float wh = (float)((double)s.pre_w / 2.0);
+    const float hh = (float)((double)s.pre_h / 2.0);
+    for (int i = tid; i < nvy * nvx; i += kThreads) {
+      const int ry = i / nvx;
+      const int rx = i - ry * nvx;
+      const int px = s.post_flip ? (s.post_w - 1 - (x0 + rx)) : (x0 + rx);
+      const float dxf = __fsub_rn((float)(long long)(s.post_x + px), twh);
+      const float dyf = __fsub_rn((float)(long long)(s.post_y + y0 + ry), thh);
+      const float fx = __fadd_rn(__fadd_rn(__fmul_rn(s.mx[0], dxf), __fmul_rn(s.mx[1], dyf)), s.mx[2]);
+      const float fy = __fadd_rn(__fadd_rn(__fmul_rn(s.mx[3], dxf), __fmul_rn(s.mx[4], dyf)), s.mx[5]);
+      const long long ax = (long long)__dadd_rn(__dadd_rn((double)fx, 0.5), (double)wh);
+      const long long ay = (long long)__dadd_rn(__dadd_rn((double)fy, 0.5), (double)hh);
+      uint8_t* q = sm.outq + (ry * kTileW + rx) * C;
+      if (ax < 0 || ay < 0 || ax >= s.pre_w || ay >= s.pre_h) {
+        for (int ch = 0; ch < C; ch++) {
+          q[ch] = 0;
+        }
+      } else {
+        const int sx = s.pre_x + (s.pre_flip ? (s.pre_w - 1 - (int)ax) : (int)ax);
+        const int sy = s.pre_y + (int)ay;
+        const uint8_t* g = s.src + ((size_t)sy * s.src_w + sx) * C;
+        for (int ch = 0; ch < C; ch++) {
+          q[ch] = __ldg(g + ch);
         }
       }
-    } else {
-      const int rowlen = nvx * C;
-      for (int i = tid; i < nvy * rowlen; i += kThreads) {
-        const int ry = i / rowlen;
-        const int j = i - ry * rowlen;
-        const int rx = j / C;
-        const int ch = j - rx * C;
-        const int px = s.post_flip ? (s.post_w - 1 - (x0 + rx)) : (x0 + rx);
-        const int gx = s.post_x + px;
-        const int gy = s.post_y + y0 + ry;
-        const int sx = s.pre_x + (s.pre_flip ? (s.pre_w - 1 - gx) : gx);
-        const int sy = s.pre_y + gy;
-        sm.outq[(ry * kTileW + rx) * C + ch] = __ldg(s.src + ((size_t)sy * s.src_w + sx) * C + ch);
-      }
+    }
+  } else {
+    const int rowlen = nvx * C;
+    for (int i = tid; i < nvy * rowlen; i += kThreads) {
+      const int ry = i / rowlen;
+      const int j = i - ry * rowlen;
+      const int rx = j / C;
+      const int ch = j - rx * C;
+      const int px = s.post_flip ? (s.post_w - 1 - (x0 + rx)) : (x0 + rx);
+      const int gx = s.post_x + px;
+      const int gy = s.post_y + y0 + ry;
+      const int sx = s.pre_x + (s.pre_flip ? (s.pre_w - 1 - gx) : gx);
+      const int sy = s.pre_y + gy;
+      sm.outq[(ry * kTileW + rx) * C + ch] = __ldg(s.src + ((size_t)sy * s.src_w + sx) * C + ch);
     }
   }
   __syncthreads();
 
   // ---- write the tile: cast values, pad outside the post window -------------
-  const int co = p.c_out;
   const int ny = y1 - y0;
   const int L = (x1 - x0) * co;
   auto pixel = [&](int ry, int j) -> int {
     const int rx = j / co;
     const int ch = j - rx * co;
-    if (has_valid && (y0 + ry) < s.post_h && (x0 + rx) < s.post_w) {
+    if ((y0 + ry) < s.post_h && (x0 + rx) < s.post_w) {
       const uint8_t* q = sm.outq + (ry * kTileW + rx) * C;
       if (p.gray) {
         int v = ((int)q[0] * p.gray_m[0] + (int)q[1] * p.gray_m[1] + (int)q[2] * p.gray_m[2] + p.gray_bias) / 65536;
@@ -336,7 +454,7 @@ __global__ void __launch_bounds__(kThreads, 2) fused_batch_kernel(const LaunchPa
     return p.pad_px;
   };
   if (p.out_f32) {
-    const float* lut = has_valid ? sm.lut : p.lut;
+    const float* lut = sm.lut;
     auto value = [&](int ry, int j) -> float {
       const int ch = j % co;
       return lut[ch * 256 + pixel(ry, j)];
@@ -377,17 +495,17 @@ __global__ void __launch_bounds__(kThreads, 2) fused_batch_kernel(const LaunchPa
 
 } // namespace
 
-size_t fused_batch_smem_bytes(const LaunchParams& p, bool any_resize) {
-  size_t b = (size_t)p.c_out * 256 * sizeof(float) + kTileH * kTileW * 4 +
-      2 * kTileH * sizeof(int) + 2 * kTileW * sizeof(int);
-  if (any_resize) {
-    b += kWeightFloats * sizeof(float) + kMidFloats * sizeof(float) + kSrcTileBytes;
-  }
-  return b;
+size_t fused_batch_smem_bytes(const LaunchParams& p) {
+  size_t off = (size_t)p.c_out * 256 * sizeof(float) + kTileH * kTileW * 4 + 2 * kTileH * sizeof(int) +
+      2 * kTileW * sizeof(int) + kMaxStagedRows * sizeof(int2) + 16;
+  off = align16(off + (size_t)p.weight_floats * sizeof(float));
+  off = align16(off + (size_t)p.mid_float4s * 16);
+  off += (size_t)p.src_tile_bytes;
+  return off + 16;
 }
 
-cudaError_t launch_fused_batch(const LaunchParams& p, bool any_resize, cudaStream_t stream) {
-  const size_t smem = fused_batch_smem_bytes(p, any_resize);
+cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream) {
+  const size_t smem = fused_batch_smem_bytes(p);
   static thread_local int configured_device = -1;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -395,9 +513,13 @@ cudaError_t launch_fused_batch(const LaunchParams& p, bool any_resize, cudaStrea
     return e;
   }
   if (configured_device != dev) {
+    LaunchParams worst = p;
+    worst.c_out = 4;
+    worst.weight_floats = kWeightFloats;
+    worst.mid_float4s = kMidFloats / 4;
+    worst.src_tile_bytes = kSrcTileBytes;
     e = cudaFuncSetAttribute(
-        fused_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-        (int)fused_batch_smem_bytes(p, true) + 1024);
+        fused_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_batch_smem_bytes(worst));
     if (e != cudaSuccess) {
       return e;
     }
@@ -410,7 +532,7 @@ cudaError_t launch_fused_batch(const LaunchParams& p, bool any_resize, cudaStrea
   if (blocks > 0x7fffffffULL) {
     return cudaErrorInvalidConfiguration;
   }
-  fused_batch_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p, any_resize ? 1 : 0);
+  fused_batch_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -426,6 +548,25 @@ AxisPlan plan_axis(int32_t n_src, int32_t n_dst, int32_t sub) {
   const long long span = ((long long)sub * n_src + n_dst - 1) / n_dst;
   a.extent = (int32_t)(span + 2 * r + 3);
   return a;
+}
+
+PassNeed plan_pass(
+    const AxisPlan& ay, const AxisPlan& ax, int32_t sub_h, int32_t sub_w, int32_t pre_h, int32_t pre_w, int32_t channels,
+    bool& fits) {
+  const long long rows = ay.extent < pre_h ? ay.extent : pre_h;
+  const long long cols = ax.extent < pre_w ? ax.extent : pre_w;
+  const long long wbytes = cols * channels;
+  const long long pitch = (wbytes + 49 + 15) & ~15LL;   // covers both staging layouts
+  const long long nwords = (wbytes + 6) / 4 + 1;
+  const long long src = rows * pitch;
+  const long long mid4 = 16 * nwords;
+  const long long wts = (long long)sub_h * ay.cap + (long long)sub_w * ax.cap;
+  fits = src <= kSrcTileBytes && mid4 * 4 <= kMidFloats && wts <= kWeightFloats && rows <= kMaxStagedRows;
+  PassNeed n;
+  n.src_bytes = (int32_t)src;
+  n.mid_float4s = (int32_t)mid4;
+  n.weight_floats = (int32_t)wts;
+  return n;
 }
 
 } // namespace mlxd

@@ -12,11 +12,13 @@ constexpr int kTileH = 16;    // output rows per CTA
 constexpr int kTileW = 64;    // output pixels per row per CTA
 constexpr int kThreads = 256;
 
-// Shared-memory budget of the resize path (bytes / floats).  Two CTAs of this
-// size fit in one SM's 227 KB.
-constexpr int kSrcTileBytes = 36 * 1024;   // staged source footprint, uint8
-constexpr int kMidFloats = 10 * 1024;      // vertically filtered rows, float32
+// Upper bounds on the shared memory one resize pass may ask for.  The planner
+// shrinks the pass (sub_h x sub_w outputs) until its footprint fits; a launch
+// then allocates only the largest need among its samples.
+constexpr int kSrcTileBytes = 48 * 1024;   // staged source footprint, uint8
+constexpr int kMidFloats = 12 * 1024;      // vertically filtered values, float32
 constexpr int kWeightFloats = 2 * 1024;    // tap weights of both axes
+constexpr int kMaxStagedRows = 192;        // source rows per pass
 
 enum Mode : int32_t { kModeCopy = 0, kModeResize = 1, kModeAffine = 2 };
 
@@ -54,19 +56,35 @@ struct LaunchParams {
   const float* lut;           // [c_out][256] cast table, device
   int32_t pad_px;             // pad value as a pixel
   int32_t* status;            // device word, non-zero once a self-check failed
+  // shared memory of the resize passes (0 when no sample resizes)
+  int32_t src_tile_bytes;
+  int32_t mid_float4s;
+  int32_t weight_floats;
+};
+
+// Shared-memory need of one resize pass, from the planner's conservative bounds.
+struct PassNeed {
+  int32_t src_bytes;
+  int32_t mid_float4s;
+  int32_t weight_floats;
 };
 
 // Bytes of dynamic shared memory the kernel needs for these parameters.
-size_t fused_batch_smem_bytes(const LaunchParams& p, bool any_resize);
+size_t fused_batch_smem_bytes(const LaunchParams& p);
 
-cudaError_t launch_fused_batch(const LaunchParams& p, bool any_resize, cudaStream_t stream);
+cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream);
 
-// Conservative footprint check used by the host planner: can one pass over
-// sub_h x sub_w geometric-output pixels be staged for this axis pair?
+// Conservative per-axis bounds used by the host planner.
 struct AxisPlan {
   int32_t cap;      // tap-count bound
   int32_t extent;   // bound on source samples touched by `sub` outputs
 };
 AxisPlan plan_axis(int32_t n_src, int32_t n_dst, int32_t sub);
+
+// Bound on the shared memory of a pass over sub_h x sub_w outputs of an axis
+// pair; `fits` tells whether it respects the limits above.
+PassNeed plan_pass(
+    const AxisPlan& ay, const AxisPlan& ax, int32_t sub_h, int32_t sub_w, int32_t pre_h, int32_t pre_w, int32_t channels,
+    bool& fits);
 
 } // namespace mlxd
