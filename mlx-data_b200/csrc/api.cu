@@ -254,6 +254,8 @@ int mlxd_fused_batch_on_stream(
   p.src_tile_bytes = need.src_bytes;
   p.mid_float4s = need.mid_float4s;
   p.weight_floats = need.weight_floats;
+  p.u_cap = need.u_cap;
+  choose_kernel(p, need);
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)b.slot_h * b.slot_w * p.c_out * esize;
   uint64_t algo_src = 0;

@@ -105,7 +105,10 @@ static int plan_resize(DevSample& s, int C, int i, PassNeed& need) {
     const AxisPlan ay = plan_axis(s.pre_h, s.geom_h, sub_h);
     const AxisPlan ax = plan_axis(s.pre_w, s.geom_w, sub_w);
     bool fits = false;
-    const PassNeed n = plan_pass(ay, ax, sub_h, sub_w, s.pre_h, s.pre_w, C, fits);
+    PassNeed n = plan_pass(ay, ax, sub_h, sub_w, s.pre_h, s.pre_w, C, fits);
+    // source rows feeding one group of (at most) four adjacent output rows
+    n.u_cap = plan_axis(s.pre_h, s.geom_h, std::min(4, sub_h)).extent;
+    fits = fits && n.u_cap <= kMaxStagedRows;
     if (fits) {
       s.sub_h = sub_h;
       s.sub_w = sub_w;
@@ -114,6 +117,7 @@ static int plan_resize(DevSample& s, int C, int i, PassNeed& need) {
       need.src_bytes = std::max(need.src_bytes, n.src_bytes);
       need.mid_float4s = std::max(need.mid_float4s, n.mid_float4s);
       need.weight_floats = std::max(need.weight_floats, n.weight_floats);
+      need.u_cap = std::max(need.u_cap, n.u_cap);
       return MLXD_OK;
     }
     if (sub_h > 4) {
@@ -135,7 +139,7 @@ static int plan_resize(DevSample& s, int C, int i, PassNeed& need) {
 int plan_samples(
     const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b,
     std::vector<DevSample>& out, PassNeed& need) {
-  need = PassNeed{0, 0, 0};
+  need = PassNeed{0, 0, 0, 0, 0};
   out.resize(n);
   for (int i = 0; i < n; i++) {
     const mlxd_sample_desc& d = samples[i];
@@ -174,6 +178,9 @@ int plan_samples(
         rc = plan_resize(s, b->channels, i, need);
         if (rc != MLXD_OK) {
           return rc;
+        }
+        if (s.pre_flip) {
+          need.needs_generic = 1;
         }
       }
     } else if (d.geom == MLXD_GEOM_AFFINE) {
@@ -339,6 +346,8 @@ int enqueue_on_lane(
   p.src_tile_bytes = need.src_bytes;
   p.mid_float4s = need.mid_float4s;
   p.weight_floats = need.weight_floats;
+  p.u_cap = need.u_cap;
+  choose_kernel(p, need);
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)batch->slot_h * batch->slot_w * p.c_out * esize;
   const size_t out_bytes = slot_bytes * n;

@@ -15,60 +15,7 @@
 //   cast               README.md:55-57 (x.astype(float32) / 255 and its normalised form)
 #include "fused_batch.h"
 
-namespace mlxd {
-
-namespace {
-
-__device__ __forceinline__ int clampi(int v, int lo, int hi) {
-  return v < lo ? lo : (v > hi ? hi : v);
-}
-
-// Tap range and normalised triangle weights of output sample o of an n -> m
-// axis.  Every step is a single correctly rounded float32 operation in a fixed
-// order, so the weights do not depend on the compiler's contraction choices:
-//   ratio = n / m, u = (o + 0.5) * ratio - 0.5, tent radius max(1, ratio),
-//   k_i = max(0, 1 - |i - u| * min(1, m / n)), w_i = k_i / sum(k).
-__device__ __forceinline__ void axis_taps(
-    int n, int m, int o, int cap, int& first, int& count, float* w) {
-  if (n == m) {
-    first = o;
-    count = 1;
-    w[0] = 1.0f;
-    return;
-  }
-  const float ratio = __fdiv_rn((float)n, (float)m);
-  const float scale = __fdiv_rn((float)m, (float)n);
-  const float fs = scale < 1.0f ? scale : 1.0f;
-  const float radius = ratio > 1.0f ? ratio : 1.0f;
-  const float u = __fsub_rn(__fmul_rn(__fadd_rn((float)o, 0.5f), ratio), 0.5f);
-  const int lo = (int)ceilf(__fsub_rn(u, radius));
-  const int hi = (int)floorf(__fadd_rn(u, radius));
-  int cnt = hi - lo + 1;
-  cnt = cnt > cap ? cap : cnt;
-  float sum = 0.0f;
-  for (int k = 0; k < cnt; k++) {
-    float d = fabsf(__fsub_rn((float)(lo + k), u));
-    float v = __fsub_rn(1.0f, __fmul_rn(d, fs));
-    v = v > 0.0f ? v : 0.0f;
-    w[k] = v;
-    sum = __fadd_rn(sum, v);
-  }
-  for (int k = 0; k < cnt; k++) {
-    w[k] = __fdiv_rn(w[k], sum);
-  }
-  first = lo;
-  count = cnt;
-}
-
-__device__ __forceinline__ int quantise(float acc) {
-  const float r = __fadd_rn(acc, 0.5f);
-  return r < 0.0f ? 0 : (r > 255.0f ? 255 : (int)r);
-}
-
-} // namespace
-} // namespace mlxd
-
-#include "resize_fast.cuh"
+#include "kernel_common.cuh"
 
 namespace mlxd {
 namespace {
@@ -80,7 +27,9 @@ struct SmemLayout {
   int* vcount;
   int* hfirst;
   int* hcount;
-  int2* rowinfo;
+  int2* urow;
+  float4* uw;
+  int* ucount;
   uint64_t* bar;
   float* wts;
   float* mid;
@@ -106,8 +55,12 @@ __device__ __forceinline__ SmemLayout carve(unsigned char* base, const LaunchPar
   off += kTileW * sizeof(int);
   l.hcount = reinterpret_cast<int*>(base + off);
   off += kTileW * sizeof(int);
-  l.rowinfo = reinterpret_cast<int2*>(base + off);
-  off += kMaxStagedRows * sizeof(int2);
+  l.uw = reinterpret_cast<float4*>(base + off);
+  off += (size_t)4 * p.u_cap * sizeof(float4);
+  l.urow = reinterpret_cast<int2*>(base + off);
+  off += (size_t)4 * p.u_cap * sizeof(int2);
+  l.ucount = reinterpret_cast<int*>(base + off);
+  off += 16;
   l.bar = reinterpret_cast<uint64_t*>(base + off);
   off += 16;
   l.wts = reinterpret_cast<float*>(base + off);
@@ -284,35 +237,7 @@ __device__ void resize_region(
   }
 }
 
-template <int C>
-__device__ void resize_tile_fast(
-    const DevSample& s, const LaunchParams& p, const SmemLayout& sm,
-    int gy_lo, int gy_hi, int gx_lo, int gx_hi) {
-  fast::Layout fl;
-  fl.lut = sm.lut;
-  fl.vfirst = sm.vfirst;
-  fl.vcount = sm.vcount;
-  fl.hfirst = sm.hfirst;
-  fl.hcount = sm.hcount;
-  fl.rowinfo = sm.rowinfo;
-  fl.wts = sm.wts;
-  fl.mid = reinterpret_cast<float4*>(sm.mid);
-  fl.srct = sm.srct;
-  fl.bar = sm.bar;
-  if (threadIdx.x == 0) {
-    fast::mbar_init(sm.bar, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
-  unsigned parity = 0;
-  for (int by = gy_lo; by < gy_hi; by += s.sub_h) {
-    for (int bx = gx_lo; bx < gx_hi; bx += s.sub_w) {
-      fast::resize_pass<C>(s, p, fl, parity, by, bx, min(s.sub_h, gy_hi - by), min(s.sub_w, gx_hi - bx));
-    }
-  }
-}
-
-__global__ void __launch_bounds__(kThreads, 3) fused_batch_kernel(const LaunchParams p) {
+__global__ void __launch_bounds__(kThreads, 2) fused_batch_kernel(const LaunchParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const SmemLayout sm = carve(smem_raw, p);
   const int tid = threadIdx.x;
@@ -369,20 +294,6 @@ __global__ void __launch_bounds__(kThreads, 3) fused_batch_kernel(const LaunchPa
     } else {
       gx_lo = s.post_x + s.post_w - vx1;
       gx_hi = s.post_x + s.post_w - x0;
-    }
-    const bool fast_ok = p.out_f32 && !p.gray && !s.pre_flip && (C == 1 || C == 3 || C == 4);
-    if (fast_ok) {
-      if (C == 3) {
-        resize_tile_fast<3>(s, p, sm, s.post_y + y0, s.post_y + vy1, gx_lo, gx_hi);
-      } else if (C == 1) {
-        resize_tile_fast<1>(s, p, sm, s.post_y + y0, s.post_y + vy1, gx_lo, gx_hi);
-      } else {
-        resize_tile_fast<4>(s, p, sm, s.post_y + y0, s.post_y + vy1, gx_lo, gx_hi);
-      }
-      // pad the part of the tile outside the post window
-      fill_rect_f32(reinterpret_cast<float*>(s.dst), s.slot_w, co, vy1, y1, x0, x1, padf);
-      fill_rect_f32(reinterpret_cast<float*>(s.dst), s.slot_w, co, y0, vy1, vx1, x1, padf);
-      return;
     }
     resize_region(s, p, sm, y0, x0, s.post_y + y0, s.post_y + vy1, gx_lo, gx_hi);
   } else if (s.mode == kModeAffine) {
@@ -497,7 +408,7 @@ __global__ void __launch_bounds__(kThreads, 3) fused_batch_kernel(const LaunchPa
 
 size_t fused_batch_smem_bytes(const LaunchParams& p) {
   size_t off = (size_t)p.c_out * 256 * sizeof(float) + kTileH * kTileW * 4 + 2 * kTileH * sizeof(int) +
-      2 * kTileW * sizeof(int) + kMaxStagedRows * sizeof(int2) + 16;
+      2 * kTileW * sizeof(int) + (size_t)4 * p.u_cap * (sizeof(float4) + sizeof(int2)) + 16 + 16;
   off = align16(off + (size_t)p.weight_floats * sizeof(float));
   off = align16(off + (size_t)p.mid_float4s * 16);
   off += (size_t)p.src_tile_bytes;
@@ -505,6 +416,9 @@ size_t fused_batch_smem_bytes(const LaunchParams& p) {
 }
 
 cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream) {
+  if (p.use_fast) {
+    return launch_fused_fast(p, stream);
+  }
   const size_t smem = fused_batch_smem_bytes(p);
   static thread_local int configured_device = -1;
   int dev = 0;
@@ -518,6 +432,7 @@ cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream) {
     worst.weight_floats = kWeightFloats;
     worst.mid_float4s = kMidFloats / 4;
     worst.src_tile_bytes = kSrcTileBytes;
+    worst.u_cap = kMaxStagedRows;
     e = cudaFuncSetAttribute(
         fused_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_batch_smem_bytes(worst));
     if (e != cudaSuccess) {
@@ -534,6 +449,11 @@ cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream) {
   }
   fused_batch_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
   return cudaGetLastError();
+}
+
+void choose_kernel(LaunchParams& p, const PassNeed& need) {
+  const bool channels_ok = p.c_in == 1 || p.c_in == 3 || p.c_in == 4;
+  p.use_fast = (p.out_f32 && !p.gray && channels_ok && !need.needs_generic) ? 1 : 0;
 }
 
 AxisPlan plan_axis(int32_t n_src, int32_t n_dst, int32_t sub) {
@@ -566,6 +486,7 @@ PassNeed plan_pass(
   n.src_bytes = (int32_t)src;
   n.mid_float4s = (int32_t)mid4;
   n.weight_floats = (int32_t)wts;
+  n.u_cap = (int32_t)(ay.extent < pre_h + 2 * ay.cap ? ay.extent : pre_h + 2 * ay.cap);
   return n;
 }
 

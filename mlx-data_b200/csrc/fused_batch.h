@@ -60,6 +60,8 @@ struct LaunchParams {
   int32_t src_tile_bytes;
   int32_t mid_float4s;
   int32_t weight_floats;
+  int32_t u_cap;              // bound on the source rows feeding four adjacent output rows
+  int32_t use_fast;           // 1: the float32 kernel (fused_fast.cu) can run this launch
 };
 
 // Shared-memory need of one resize pass, from the planner's conservative bounds.
@@ -67,12 +69,19 @@ struct PassNeed {
   int32_t src_bytes;
   int32_t mid_float4s;
   int32_t weight_floats;
+  int32_t u_cap;
+  int32_t needs_generic;      // a sample only the generic kernel handles (mirrored source under a resize)
 };
 
 // Bytes of dynamic shared memory the kernel needs for these parameters.
 size_t fused_batch_smem_bytes(const LaunchParams& p);
 
+// Launch the float32 kernel when p.use_fast is set, else the generic one.
 cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream);
+cudaError_t launch_fused_fast(const LaunchParams& p, cudaStream_t stream);
+
+// Decide which kernel runs a launch; call after the planner filled `need`.
+void choose_kernel(LaunchParams& p, const PassNeed& need);
 
 // Conservative per-axis bounds used by the host planner.
 struct AxisPlan {

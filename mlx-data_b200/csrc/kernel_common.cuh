@@ -1,0 +1,142 @@
+// Device helpers shared by the two kernels of the library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "fused_batch.h"
+
+namespace mlxd {
+
+__device__ __forceinline__ int clampi(int v, int lo, int hi) {
+  return v < lo ? lo : (v > hi ? hi : v);
+}
+
+// Geometry of one axis of a triangle-filter resize, n source -> m output
+// samples.  Every step is one correctly rounded float32 operation in a fixed
+// order (no contraction), so host and device agree bit for bit:
+//   ratio = n / m, u(o) = (o + 0.5) * ratio - 0.5, radius = max(1, ratio),
+//   taps i = ceil(u - radius) .. floor(u + radius),
+//   k_i = max(0, 1 - |i - u| * min(1, m / n)), w_i = k_i / sum(k).
+struct Axis {
+  float ratio, fs, radius;
+  bool identity;
+};
+
+__device__ __forceinline__ Axis make_axis(int n, int m) {
+  Axis a;
+  a.identity = n == m;
+  a.ratio = __fdiv_rn((float)n, (float)m);
+  const float scale = __fdiv_rn((float)m, (float)n);
+  a.fs = scale < 1.0f ? scale : 1.0f;
+  a.radius = a.ratio > 1.0f ? a.ratio : 1.0f;
+  return a;
+}
+
+__device__ __forceinline__ float axis_center(const Axis& a, int o) {
+  return __fsub_rn(__fmul_rn(__fadd_rn((float)o, 0.5f), a.ratio), 0.5f);
+}
+
+// Un-clamped first and last tap of output sample o.
+__device__ __forceinline__ void axis_range(const Axis& a, int o, int& lo, int& hi) {
+  if (a.identity) {
+    lo = hi = o;
+    return;
+  }
+  const float u = axis_center(a, o);
+  lo = (int)ceilf(__fsub_rn(u, a.radius));
+  hi = (int)floorf(__fadd_rn(u, a.radius));
+}
+
+// Un-normalised tent value of source sample i for the output centred at u.
+__device__ __forceinline__ float axis_tent(const Axis& a, float u, int i) {
+  const float d = fabsf(__fsub_rn((float)i, u));
+  const float v = __fsub_rn(1.0f, __fmul_rn(d, a.fs));
+  return v > 0.0f ? v : 0.0f;
+}
+
+// Tap range and normalised weights of output sample o; at most cap taps.
+__device__ __forceinline__ void axis_taps(
+    int n, int m, int o, int cap, int& first, int& count, float* w) {
+  if (n == m) {
+    first = o;
+    count = 1;
+    w[0] = 1.0f;
+    return;
+  }
+  const Axis a = make_axis(n, m);
+  const float u = axis_center(a, o);
+  int lo, hi;
+  axis_range(a, o, lo, hi);
+  int cnt = hi - lo + 1;
+  cnt = cnt > cap ? cap : cnt;
+  float sum = 0.0f;
+  for (int k = 0; k < cnt; k++) {
+    const float v = axis_tent(a, u, lo + k);
+    w[k] = v;
+    sum = __fadd_rn(sum, v);
+  }
+  for (int k = 0; k < cnt; k++) {
+    w[k] = __fdiv_rn(w[k], sum);
+  }
+  first = lo;
+  count = cnt;
+}
+
+__device__ __forceinline__ int quantise(float acc) {
+  const float r = __fadd_rn(acc, 0.5f);
+  return r < 0.0f ? 0 : (r > 255.0f ? 255 : (int)r);
+}
+
+template <int CO>
+__device__ __forceinline__ float pad_pick(const float (&padf)[4], int m) {
+  if (CO == 1) {
+    return padf[0];
+  }
+  float v = padf[0];
+  v = m == 1 ? padf[1] : v;
+  v = m == 2 ? padf[2] : v;
+  if (CO > 3) {
+    v = m == 3 ? padf[3] : v;
+  }
+  return v;
+}
+
+// Pad value (already cast) into the rectangle [ya, yb) x [xa, xb) of a slot
+// with CO channels, 16-byte stores wherever the row segment allows.
+template <int CO>
+__device__ __forceinline__ void fill_rect_f32(
+    float* base, int slot_w, int ya, int yb, int xa, int xb, const float (&padf)[4]) {
+  if (ya >= yb || xa >= xb) {
+    return;
+  }
+  const int L = (xb - xa) * CO;
+  const int Q = ((L + 3) >> 2) + 2;
+  const int ny = yb - ya;
+  for (int i = threadIdx.x; i < ny * Q; i += kThreads) {
+    const int ry = i / Q;
+    const int q = i - ry * Q;
+    float* rowp = base + ((size_t)(ya + ry) * slot_w + xa) * CO;
+    const int mis = (int)((reinterpret_cast<uintptr_t>(rowp) >> 2) & 3);
+    int head = (4 - mis) & 3;
+    head = head > L ? L : head;
+    const int nvec = (L - head) >> 2;
+    if (q == 0) {
+      for (int j = 0; j < head; j++) {
+        rowp[j] = pad_pick<CO>(padf, j % CO);
+      }
+    } else if (q <= nvec) {
+      const int j = head + 4 * (q - 1);
+      const int m = j % CO;
+      *reinterpret_cast<float4*>(rowp + j) = make_float4(
+          pad_pick<CO>(padf, m), pad_pick<CO>(padf, (m + 1) % CO), pad_pick<CO>(padf, (m + 2) % CO),
+          pad_pick<CO>(padf, (m + 3) % CO));
+    } else if (q == nvec + 1) {
+      for (int j = head + 4 * nvec; j < L; j++) {
+        rowp[j] = pad_pick<CO>(padf, j % CO);
+      }
+    }
+  }
+}
+
+} // namespace mlxd
