@@ -136,13 +136,8 @@ static int plan_resize(DevSample& s, int C, int i, PassNeed& need) {
   }
 }
 
-int plan_samples(
-    const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b,
-    std::vector<DevSample>& out, PassNeed& need) {
-  need = PassNeed{0, 0, 0, 0, 0};
-  out.resize(n);
-  for (int i = 0; i < n; i++) {
-    const mlxd_sample_desc& d = samples[i];
+int plan_one_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, DevSample& out, PassNeed& need) {
+  {
     int rc = check_sample(d, i, b, b->slot_h, b->slot_w);
     if (rc != MLXD_OK) {
       return rc;
@@ -194,7 +189,21 @@ int plan_samples(
       s.post_flip ^= 1;
       s.post_x = s.geom_w - s.post_x - s.post_w;
     }
-    out[i] = s;
+    out = s;
+  }
+  return MLXD_OK;
+}
+
+int plan_samples(
+    const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b,
+    std::vector<DevSample>& out, PassNeed& need) {
+  need = PassNeed{0, 0, 0, 0, 0};
+  out.resize(n);
+  for (int i = 0; i < n; i++) {
+    const int rc = plan_one_sample(samples[i], i, b, out[i], need);
+    if (rc != MLXD_OK) {
+      return rc;
+    }
   }
   return MLXD_OK;
 }
@@ -237,6 +246,22 @@ void needed_region(const DevSample& s, int margin, int32_t& r0, int32_t& r1, int
   c1 = (int32_t)(s.pre_x + chi);
 }
 
+void compute_cast_table(const mlxd_batch_desc* b, int c_out, float* table) {
+  // Every entry is the chain of float32 operations numpy performs:
+  // float(v) / divisor, then - mean, then / std.
+  for (int c = 0; c < c_out; c++) {
+    for (int v = 0; v < 256; v++) {
+      volatile float x = (float)v;
+      volatile float q = x / b->divisor;
+      if (b->normalise) {
+        volatile float t = q - b->mean[c];
+        q = t / b->std_[c];
+      }
+      table[(size_t)c * 256 + v] = q;
+    }
+  }
+}
+
 int get_lut(mlxd_ctx* ctx, const mlxd_batch_desc* b, int c_out, const float** lut) {
   LutKey key;
   std::memset(&key, 0, sizeof(key));
@@ -253,20 +278,8 @@ int get_lut(mlxd_ctx* ctx, const mlxd_batch_desc* b, int c_out, const float** lu
     *lut = it->second;
     return MLXD_OK;
   }
-  // Every entry is the chain of float32 operations numpy performs:
-  // float(v) / divisor, then - mean, then / std.
   std::vector<float> table((size_t)c_out * 256);
-  for (int c = 0; c < c_out; c++) {
-    for (int v = 0; v < 256; v++) {
-      volatile float x = (float)v;
-      volatile float q = x / b->divisor;
-      if (key.normalise) {
-        volatile float t = q - b->mean[c];
-        q = t / b->std_[c];
-      }
-      table[(size_t)c * 256 + v] = q;
-    }
-  }
+  compute_cast_table(b, c_out, table.data());
   float* d = nullptr;
   MLXD_CUDA(cudaMalloc(&d, table.size() * sizeof(float)));
   cudaError_t e = cudaMemcpy(d, table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice);

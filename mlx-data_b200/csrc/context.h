@@ -83,6 +83,12 @@ int plan_samples(
     const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b,
     std::vector<DevSample>& out, PassNeed& need);
 
+// One sample of plan_samples; `need` accumulates the shared-memory bounds.
+int plan_one_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, DevSample& out, PassNeed& need);
+
+// The cast table of a batch descriptor: table[c * 256 + v], c < c_out.
+void compute_cast_table(const mlxd_batch_desc* b, int c_out, float* table);
+
 // Launch-wide parameters (cast table included) from a batch descriptor.
 int prepare_launch(mlxd_ctx* ctx, const mlxd_batch_desc* b, int n, LaunchParams& p);
 
