@@ -135,6 +135,34 @@ MLXD_API void mlxd_device_free(mlxd_ctx* ctx, void* p);
  * and add the elapsed device time to mlxd_stats.kernel_ns (off by default). */
 MLXD_API int mlxd_ctx_set_timing(mlxd_ctx* ctx, int on);
 
+/* The fused batch for callers that cannot allocate.  It has no counterpart in
+ * the reference.  Who needs it: a loader plug-in that runs inside a training
+ * step whose framework has handed the whole GPU to its own memory pool, a
+ * service that bans allocator calls once it is warm, a process sitting at its
+ * memory limit - for them a cudaMalloc (or a pinned-host allocation) in the
+ * data path is a failure or a stall, and the other entry points do allocate:
+ * descriptor tables, the cast table and a status word, on demand.  Here those
+ * live in a fixed array inside the library image, so the call allocates
+ * nothing on the device or the host, and needs no context.
+ *
+ * Same meaning as mlxd_fused_batch_on_stream: sources and destination are
+ * device memory (batch->src_mem == batch->dst_mem == MLXD_MEM_DEVICE), the
+ * kernel is queued on the caller's CUDA stream, the descriptors are read
+ * before the call returns.  Limits and rules:
+ *  - at most MLXD_NOALLOC_MAX_SAMPLES samples per call; more is refused with
+ *    MLXD_ERR_INVALID (split the batch, or use the allocating entry point);
+ *  - the array (about 0.15 MB) is held by every GPU that loads the library
+ *    until the process exits;
+ *  - the first call on a device looks up the array's device address; make
+ *    that first call before any stream capture;
+ *  - all calls share the one array, which keeps the previous call's contents
+ *    (the call clears what must start at zero): two calls whose kernels can
+ *    overlap on the GPU - different streams, or different host threads - race;
+ *    order them on one stream. */
+#define MLXD_NOALLOC_MAX_SAMPLES 1024
+MLXD_API int mlxd_fused_batch_noalloc(
+    int device, void* cuda_stream, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch);
+
 /* Enqueue one fused batch on a lane and return: host sources are copied to the
  * device (only the rows the chain reads), one kernel writes every slot, and a
  * host dst is copied back.  Replaces stream::Batch::next -> core::merge_batch

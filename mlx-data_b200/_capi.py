@@ -77,8 +77,9 @@ EXPORTS = [
     "mlxd_fused_batch", "mlxd_batch_wait", "mlxd_fused_batch_on_stream", "mlxd_image_resize",
     "mlxd_image_crop", "mlxd_image_hflip", "mlxd_image_affine", "mlxd_image_channel_reduction",
     "mlxd_batch_pad", "mlxd_cast_scale_normalise", "mlxd_stats_get",
-    "mlxd_device_alloc", "mlxd_device_free", "mlxd_ctx_set_timing",
+    "mlxd_device_alloc", "mlxd_device_free", "mlxd_ctx_set_timing", "mlxd_fused_batch_noalloc",
 ]
+NOALLOC_MAX_SAMPLES = 1024
 
 
 class MlxdError(RuntimeError):
@@ -126,6 +127,7 @@ def load():
     lib.mlxd_device_free.argtypes = [vp, vp]
     lib.mlxd_device_free.restype = None
     lib.mlxd_ctx_set_timing.argtypes = [vp, i32]
+    lib.mlxd_fused_batch_noalloc.argtypes = [i32, vp, vp, i32, ctypes.POINTER(BatchDesc)]
     _lib = lib
     return lib
 
@@ -156,6 +158,17 @@ def make_batch_desc(dst, slot_h, slot_w, channels, out_dtype=F32, divisor=255.0,
     b.pad_value = pad_value
     b.src_mem, b.dst_mem = src_mem, dst_mem
     return b
+
+
+def fused_batch_noalloc(device, stream, descs, batch):
+    """mlxd_fused_batch_noalloc: device-resident sources and destination, the
+    caller's CUDA stream, no context and no allocation (see include/mlxd_b200.h)."""
+    lib = load()
+    assert descs.dtype == SAMPLE_DTYPE and descs.flags.c_contiguous
+    rc = lib.mlxd_fused_batch_noalloc(device, ctypes.c_void_p(stream), descs.ctypes.data, len(descs),
+                                      ctypes.byref(batch))
+    if rc != OK:
+        raise MlxdError(rc, lib.mlxd_last_error().decode())
 
 
 class Context:
