@@ -3,6 +3,7 @@
 
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <thread>
 
@@ -405,6 +406,17 @@ int enqueue_on_lane(
     for (int i = 0; i < n; i++) {
       int32_t r0, r1, c0, c1;
       needed_region(dev[i], 2, r0, r1, c0, c1);
+      // A strided (2-D) copy moves fewer bytes but runs slower per byte than a
+      // contiguous one: trim columns only when that drops at least the
+      // configured share of every row (MLXD_TRIM_PERCENT, default 60).
+      static const int trim_percent = [] {
+        const char* v = std::getenv("MLXD_TRIM_PERCENT");
+        return v && *v ? std::atoi(v) : 60;
+      }();
+      if ((int64_t)(dev[i].src_w - (c1 - c0)) * 100 < (int64_t)trim_percent * dev[i].src_w) {
+        c0 = 0;
+        c1 = dev[i].src_w;
+      }
       // The staged block is an image of its own: rows [r0, r1), columns
       // [c0, c1) of the source, tightly packed.
       pieces[i].offset = stage_bytes;

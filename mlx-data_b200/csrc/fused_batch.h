@@ -62,6 +62,8 @@ struct LaunchParams {
   int32_t weight_floats;
   int32_t u_cap;              // bound on the source rows feeding four adjacent output rows
   int32_t use_fast;           // 1: the float32 kernel (fused_fast.cu) can run this launch
+  int32_t band_tiles;         // float32 kernel: tiles per CTA along a row band (set at launch)
+  int32_t bands_x;            // float32 kernel: CTAs per row band
 };
 
 // Shared-memory need of one resize pass, from the planner's conservative bounds.
