@@ -38,7 +38,7 @@ int make_lane(Lane** out) {
     return fail(MLXD_ERR_NOMEM, "out of host memory");
   }
   cudaError_t e = cudaStreamCreateWithFlags(&l->stream, cudaStreamNonBlocking);
-  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&l->done, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&l->done, cudaEventDisableTiming | cudaEventBlockingSync);
   for (int s = 0; s < kDescSlots && e == cudaSuccess; s++) {
     e = cudaEventCreateWithFlags(&l->desc_copied[s], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreate(&l->k_begin[s]);

@@ -513,6 +513,10 @@ void harvest_timing(mlxd_ctx* ctx, Lane& lane, int slot, bool block) {
 int wait_lane(mlxd_ctx* ctx, Lane& lane, int timeout_ms) {
   MLXD_CUDA(cudaSetDevice(ctx->device));
   const auto start = std::chrono::steady_clock::now();
+  if (timeout_ms < 0) {
+    // no deadline: block in the driver instead of polling it from every lane
+    MLXD_CUDA(cudaEventSynchronize(lane.done));
+  }
   for (;;) {
     cudaError_t e = cudaEventQuery(lane.done);
     if (e == cudaSuccess) {

@@ -230,14 +230,29 @@ mlxd_ctx* Runtime::ctx() {
   return ctx_;
 }
 
-int Runtime::lane() {
-  static thread_local int mine = -1;
-  if (mine < 0) {
-    ctx();
-    std::lock_guard<std::mutex> g(mu_);
-    mine = next_lane_++ % n_lanes_;
+int Runtime::acquire_lane() {
+  ctx();
+  std::unique_lock<std::mutex> lk(mu_);
+  if (!lanes_ready_) {
+    for (int i = n_lanes_ - 1; i >= 0; i--) {
+      free_lanes_.push_back(i);
+    }
+    lanes_ready_ = true;
   }
-  return mine;
+  lane_cv_.wait(lk, [this] { return !free_lanes_.empty(); });
+  // the lane released last is taken first: its staging buffers are already as
+  // large as the work in flight needs
+  const int ln = free_lanes_.back();
+  free_lanes_.pop_back();
+  return ln;
+}
+
+void Runtime::release_lane(int ln) {
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    free_lanes_.push_back(ln);
+  }
+  lane_cv_.notify_one();
 }
 
 Runtime::~Runtime() {}
@@ -372,9 +387,14 @@ std::shared_ptr<Array> Runtime::batch(const std::vector<LazyImage>& images, doub
     check(mlxd_fused_batch_on_stream(c, ext_stream_, descs.data(), n, &b));
     return out;
   }
-  const int ln = lane();
-  check(mlxd_fused_batch(c, ln, descs.data(), n, &b));
-  check(mlxd_batch_wait(c, ln, -1));
+  // one lane per call in flight, whatever thread makes the call
+  const int ln = acquire_lane();
+  int rc = mlxd_fused_batch(c, ln, descs.data(), n, &b);
+  if (rc == MLXD_OK) {
+    rc = mlxd_batch_wait(c, ln, -1);
+  }
+  release_lane(ln);
+  check(rc);
   return out;
 }
 

@@ -6,6 +6,7 @@
 
 #include <cstdint>
 #include <memory>
+#include <condition_variable>
 #include <mutex>
 #include <map>
 #include <vector>
@@ -87,8 +88,10 @@ class Runtime {
   static int device();
 
   mlxd_ctx* ctx();
-  // Lane of the calling thread: threads are spread round-robin over lanes.
-  int lane();
+  // Check a lane out for one call in flight (blocks while all are busy) and
+  // hand it back afterwards.
+  int acquire_lane();
+  void release_lane(int lane);
   void check(int rc) const;
 
   // Array whose storage is page-locked host memory from a recycling pool.
@@ -132,7 +135,9 @@ class Runtime {
   std::mutex mu_;
   mlxd_ctx* ctx_ = nullptr;
   int n_lanes_ = 8;
-  int next_lane_ = 0;
+  std::vector<int> free_lanes_;
+  bool lanes_ready_ = false;
+  std::condition_variable lane_cv_;
   Pool pinned_pool_;
 };
 
