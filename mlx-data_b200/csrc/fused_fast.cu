@@ -99,6 +99,14 @@ __device__ __forceinline__ void bytes_to_float2(uint32_t word, float& f0, float&
       : "f"(x0), "f"(x1), "f"(-8388608.0f));
 }
 
+// (int)(acc + 0.5) clamped to [0, 255]: the float-to-uint8 conversion truncates
+// toward zero and saturates at both ends, which is that clamp.
+__device__ __forceinline__ unsigned quantise_sat(float acc) {
+  unsigned q;
+  asm("cvt.rzi.u8.f32 %0, %1;" : "=r"(q) : "f"(__fadd_rn(acc, 0.5f)));
+  return q;
+}
+
 // Tables that change from pass to pass (a pass = one run of output columns of
 // the band); two sets, so the next pass's tables are built while the current
 // pass is still filtering horizontally.
@@ -135,11 +143,11 @@ __host__ __device__ inline size_t smem_layout(const LaunchParams& p, unsigned ch
     off += kTileW * sizeof(int);
     sm.tab[k].urow = reinterpret_cast<int2*>(base + off);
     off += (size_t)4 * p.u_cap * sizeof(int2);
-    sm.tab[k].wh = reinterpret_cast<float*>(base + off);
-    off = align16(off + (size_t)p.weight_floats * sizeof(float));
+    sm.tab[k].wh = reinterpret_cast<float*>(base + off);   // (w, w) pairs
+    off = align16(off + (size_t)p.weight_floats * 2 * sizeof(float));
   }
   sm.uw = reinterpret_cast<float4*>(base + off);
-  off += (size_t)4 * p.u_cap * sizeof(float4);
+  off += (size_t)4 * p.u_cap * 2 * sizeof(float4);
   sm.ucount = reinterpret_cast<int*>(base + off);
   off += 16;
   sm.bar = reinterpret_cast<uint64_t*>(base + off);
@@ -199,30 +207,34 @@ __device__ __forceinline__ void start_pass(
     mbar_expect_tx(sm.bar, len);
     bulk_copy(sm.srct + tid * g.pitch_s, reinterpret_cast<const void*>(ga - phase), len, sm.bar);
   }
-  // horizontal taps: one thread per (output column, tap); the normalising sum
-  // is the same increasing-order chain in every thread of a column
-  for (int i = tid; i < g.nc * s.cap_x; i += kThreads) {
-    const int x = i / s.cap_x;
-    const int k = i - x * s.cap_x;
-    int lo, hi;
-    axis_range(ax, g.bx + x, lo, hi);
-    int cnt = hi - lo + 1;
-    cnt = cnt > s.cap_x ? s.cap_x : cnt;
-    if (k == 0) {
+  // horizontal taps: one thread per output column (the last warps, which issue
+  // no copies); every weight is stored twice, side by side, so the packed
+  // multiply-add reads its (w, w) operand with one 64-bit load
+  {
+    const int x = tid - (kThreads - kTileW);
+    if (x >= 0 && x < g.nc) {
+      int lo, hi;
+      axis_range(ax, g.bx + x, lo, hi);
+      int cnt = hi - lo + 1;
+      cnt = cnt > s.cap_x ? s.cap_x : cnt;
       tab.hfirst[x] = lo;
       tab.hcount[x] = cnt;
-    }
-    if (k < cnt) {
-      float w = 1.0f;
-      if (!ax.identity) {
+      float2* w2 = reinterpret_cast<float2*>(tab.wh) + x * s.cap_x;
+      if (ax.identity) {
+        w2[0] = make_float2(1.0f, 1.0f);
+      } else {
         const float c = axis_center(ax, g.bx + x);
         float sum = 0.0f;
-        for (int j = 0; j < cnt; j++) {
-          sum = __fadd_rn(sum, axis_tent(ax, c, lo + j));
+        for (int k = 0; k < cnt; k++) {
+          const float v = axis_tent(ax, c, lo + k);
+          w2[k].x = v;
+          sum = __fadd_rn(sum, v);
         }
-        w = __fdiv_rn(axis_tent(ax, c, lo + k), sum);
+        for (int k = 0; k < cnt; k++) {
+          const float w = __fdiv_rn(w2[k].x, sum);
+          w2[k] = make_float2(w, w);
+        }
       }
-      tab.wh[i] = w;
     }
   }
   const int ngroups = (nr + 3) >> 2;
@@ -310,7 +322,8 @@ __device__ void resize_rows(
         }
         w4[r] = w;
       }
-      sm.uw[i] = make_float4(w4[0], w4[1], w4[2], w4[3]);
+      sm.uw[2 * i] = make_float4(w4[0], w4[0], w4[1], w4[1]);
+      sm.uw[2 * i + 1] = make_float4(w4[2], w4[2], w4[3], w4[3]);
     }
   }
   __syncthreads();   // ucount is read by start_pass
@@ -345,7 +358,7 @@ __device__ void resize_rows(
       for (int rg = tid >> 7; rg < ngroups; rg += kThreads >> 7) {
         const int cnt = sm.ucount[rg];
         const int2* urow = tab.urow + rg * p.u_cap;
-        const float4* uw = sm.uw + rg * p.u_cap;
+        const float4* uw = sm.uw + 2 * rg * p.u_cap;
         for (int g = tid & 127; g < cur.nwords; g += 128) {
           float a00 = 0.f, a01 = 0.f, a02 = 0.f, a03 = 0.f;
           float a10 = 0.f, a11 = 0.f, a12 = 0.f, a13 = 0.f;
@@ -353,7 +366,8 @@ __device__ void resize_rows(
           float a30 = 0.f, a31 = 0.f, a32 = 0.f, a33 = 0.f;
           for (int e = 0; e < cnt; e++) {
             const int2 ri = urow[e];
-            const float4 w = uw[e];
+            const float4 wa = uw[2 * e];       // (w0, w0, w1, w1)
+            const float4 wb = uw[2 * e + 1];   // (w2, w2, w3, w3)
             uint32_t word = srcw[ri.x + g];
             if (ri.y) {
               word = __funnelshift_r(word, srcw[ri.x + g + 1], ri.y);
@@ -361,14 +375,14 @@ __device__ void resize_rows(
             float v0, v1, v2, v3;
             bytes_to_float2<0, 1>(word, v0, v1);
             bytes_to_float2<2, 3>(word, v2, v3);
-            ffma2(a00, a01, v0, v1, w.x, w.x);
-            ffma2(a02, a03, v2, v3, w.x, w.x);
-            ffma2(a10, a11, v0, v1, w.y, w.y);
-            ffma2(a12, a13, v2, v3, w.y, w.y);
-            ffma2(a20, a21, v0, v1, w.z, w.z);
-            ffma2(a22, a23, v2, v3, w.z, w.z);
-            ffma2(a30, a31, v0, v1, w.w, w.w);
-            ffma2(a32, a33, v2, v3, w.w, w.w);
+            ffma2(a00, a01, v0, v1, wa.x, wa.y);
+            ffma2(a02, a03, v2, v3, wa.x, wa.y);
+            ffma2(a10, a11, v0, v1, wa.z, wa.w);
+            ffma2(a12, a13, v2, v3, wa.z, wa.w);
+            ffma2(a20, a21, v0, v1, wb.x, wb.y);
+            ffma2(a22, a23, v2, v3, wb.x, wb.y);
+            ffma2(a30, a31, v0, v1, wb.z, wb.w);
+            ffma2(a32, a33, v2, v3, wb.z, wb.w);
           }
           // planar store: column (px, ch) of group rg -> mid[(rg * C + ch) * ncols + px]
           const int jb = 4 * g - cur.common;
@@ -438,23 +452,23 @@ __device__ void resize_rows(
         const int ch = rem - x * C;
         const int f = tab.hfirst[x];
         const int cnt = tab.hcount[x];
-        const float* w = tab.wh + x * s.cap_x;
+        const float2* w = reinterpret_cast<const float2*>(tab.wh) + x * s.cap_x;
         const float4* col = sm.mid + (rg * C + ch) * cur.ncols;
         float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
         if (!cur.edge_x) {
           const float4* c0 = col + (f - cur.clo);
           for (int k = 0; k < cnt; k++) {
             const float4 v = c0[k];
-            const float wk = w[k];
-            ffma2(a0, a1, v.x, v.y, wk, wk);
-            ffma2(a2, a3, v.z, v.w, wk, wk);
+            const float2 wk = w[k];
+            ffma2(a0, a1, v.x, v.y, wk.x, wk.y);
+            ffma2(a2, a3, v.z, v.w, wk.x, wk.y);
           }
         } else {
           for (int k = 0; k < cnt; k++) {
             const float4 v = col[clampi(f + k, 0, s.pre_w - 1) - cur.clo];
-            const float wk = w[k];
-            ffma2(a0, a1, v.x, v.y, wk, wk);
-            ffma2(a2, a3, v.z, v.w, wk, wk);
+            const float2 wk = w[k];
+            ffma2(a0, a1, v.x, v.y, wk.x, wk.y);
+            ffma2(a2, a3, v.z, v.w, wk.x, wk.y);
           }
         }
         int px = cur.bx + x - s.post_x;
@@ -465,10 +479,10 @@ __device__ void resize_rows(
         const float* lut = sm.lut + ch * 256;
         float* dst = base + ((size_t)oy * s.slot_w + px) * C + ch;
         const int left = nr - rg * 4;
-        dst[0] = lut[quantise(a0)];
-        if (left > 1) dst[row_stride] = lut[quantise(a1)];
-        if (left > 2) dst[2 * row_stride] = lut[quantise(a2)];
-        if (left > 3) dst[3 * row_stride] = lut[quantise(a3)];
+        dst[0] = lut[quantise_sat(a0)];
+        if (left > 1) dst[row_stride] = lut[quantise_sat(a1)];
+        if (left > 2) dst[2 * row_stride] = lut[quantise_sat(a2)];
+        if (left > 3) dst[3 * row_stride] = lut[quantise_sat(a3)];
       }
     }
     if (!more) {
