@@ -355,11 +355,26 @@ __device__ void resize_rows(
     // ---- vertical filter: thread = (source word, group of four output rows) -----
     {
       const uint32_t* srcw = reinterpret_cast<const uint32_t*>(sm.srct);
-      for (int rg = tid >> 7; rg < ngroups; rg += kThreads >> 7) {
-        const int cnt = sm.ucount[rg];
-        const int2* urow = tab.urow + rg * p.u_cap;
-        const float4* uw = sm.uw + 2 * rg * p.u_cap;
-        for (int g = tid & 127; g < cur.nwords; g += 128) {
+      // every thread owns one source word (four byte columns) and walks the row
+      // groups with a stride of two; where its columns land in the planar
+      // buffer does not depend on the group
+      for (int g = tid & 127; g < cur.nwords; g += 128) {
+        int off0, off1, off2, off3;
+        {
+          const int jb = 4 * g - cur.common;
+          int j = jb;
+          off0 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
+          j = jb + 1;
+          off1 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
+          j = jb + 2;
+          off2 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
+          j = jb + 3;
+          off3 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
+        }
+        for (int rg = tid >> 7; rg < ngroups; rg += kThreads >> 7) {
+          const int cnt = sm.ucount[rg];
+          const int2* urow = tab.urow + rg * p.u_cap;
+          const float4* uw = sm.uw + 2 * rg * p.u_cap;
           float a00 = 0.f, a01 = 0.f, a02 = 0.f, a03 = 0.f;
           float a10 = 0.f, a11 = 0.f, a12 = 0.f, a13 = 0.f;
           float a20 = 0.f, a21 = 0.f, a22 = 0.f, a23 = 0.f;
@@ -385,36 +400,11 @@ __device__ void resize_rows(
             ffma2(a32, a33, v2, v3, wb.z, wb.w);
           }
           // planar store: column (px, ch) of group rg -> mid[(rg * C + ch) * ncols + px]
-          const int jb = 4 * g - cur.common;
           float4* plane = sm.mid + rg * C * cur.ncols;
-          {
-            const int j = jb;
-            if (j >= 0 && j < cur.wbytes) {
-              const int px = j / C;
-              plane[(j - px * C) * cur.ncols + px] = make_float4(a00, a10, a20, a30);
-            }
-          }
-          {
-            const int j = jb + 1;
-            if (j >= 0 && j < cur.wbytes) {
-              const int px = j / C;
-              plane[(j - px * C) * cur.ncols + px] = make_float4(a01, a11, a21, a31);
-            }
-          }
-          {
-            const int j = jb + 2;
-            if (j >= 0 && j < cur.wbytes) {
-              const int px = j / C;
-              plane[(j - px * C) * cur.ncols + px] = make_float4(a02, a12, a22, a32);
-            }
-          }
-          {
-            const int j = jb + 3;
-            if (j >= 0 && j < cur.wbytes) {
-              const int px = j / C;
-              plane[(j - px * C) * cur.ncols + px] = make_float4(a03, a13, a23, a33);
-            }
-          }
+          if (off0 >= 0) plane[off0] = make_float4(a00, a10, a20, a30);
+          if (off1 >= 0) plane[off1] = make_float4(a01, a11, a21, a31);
+          if (off2 >= 0) plane[off2] = make_float4(a02, a12, a22, a32);
+          if (off3 >= 0) plane[off3] = make_float4(a03, a13, a23, a33);
         }
       }
     }
