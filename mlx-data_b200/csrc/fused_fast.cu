@@ -71,32 +71,35 @@ __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// d = a * b + d on two float lanes with one instruction (each lane is an IEEE
-// fused multiply-add, identical to two fmaf calls).
-__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
-  asm("{\n\t.reg .b64 ra, rb, rc;\n\t"
-      "mov.b64 ra, {%2, %3};\n\t"
-      "mov.b64 rb, {%4, %5};\n\t"
-      "mov.b64 rc, {%0, %1};\n\t"
-      "fma.rn.f32x2 rc, ra, rb, rc;\n\t"
-      "mov.b64 {%0, %1}, rc;\n\t}"
-      : "+f"(d0), "+f"(d1)
-      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+// Two float lanes in one 64-bit register, the operand form of the packed
+// instructions; keeping values packed avoids repacking moves around them.
+typedef unsigned long long f32x2;
+
+// d = a * b + d on both lanes (each lane is an IEEE fused multiply-add,
+// identical to fmaf).
+__device__ __forceinline__ void ffma2(f32x2& d, f32x2 a, f32x2 b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
 }
 
-// Two bytes of a word as floats, exactly: each byte is placed in the mantissa
-// of 2^23 and 2^23 is subtracted (one packed add for both).
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+// Bytes B0 and B1 of a word as two packed floats, exactly: each byte is placed
+// in the mantissa of 2^23 and 2^23 is subtracted (one packed add for both).
 template <int B0, int B1>
-__device__ __forceinline__ void bytes_to_float2(uint32_t word, float& f0, float& f1) {
+__device__ __forceinline__ f32x2 bytes_to_f32x2(uint32_t word, f32x2 minus_two23) {
   const float x0 = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540u + B0));
   const float x1 = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540u + B1));
-  asm("{\n\t.reg .b64 ra, rb, rc;\n\t"
-      "mov.b64 ra, {%2, %3};\n\t"
-      "mov.b64 rb, {%4, %4};\n\t"
-      "add.rn.f32x2 rc, ra, rb;\n\t"
-      "mov.b64 {%0, %1}, rc;\n\t}"
-      : "=f"(f0), "=f"(f1)
-      : "f"(x0), "f"(x1), "f"(-8388608.0f));
+  f32x2 r = pack2(x0, x1);
+  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(r) : "l"(minus_two23));
+  return r;
 }
 
 // (int)(acc + 0.5) clamped to [0, 255]: the float-to-uint8 conversion truncates
@@ -107,6 +110,89 @@ __device__ __forceinline__ unsigned quantise_sat(float acc) {
   return q;
 }
 
+// Shared-memory loads by 32-bit shared-space address plus a constant offset.
+// Spelling the inner loops with these keeps their address arithmetic to the
+// pointer increments written out in the loops.
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_u32(unsigned a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+  return v;
+}
+
+template <int OFF>
+__device__ __forceinline__ void lds_v2u32(unsigned a, uint32_t& x, uint32_t& y) {
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(x), "=r"(y) : "r"(a), "n"(OFF));
+}
+
+template <int OFF>
+__device__ __forceinline__ f32x2 lds_u64(unsigned a) {
+  f32x2 v;
+  asm volatile("ld.shared.u64 %0, [%1+%2];" : "=l"(v) : "r"(a), "n"(OFF));
+  return v;
+}
+
+template <int OFF>
+__device__ __forceinline__ void lds_v2u64(unsigned a, f32x2& x, f32x2& y) {
+  asm volatile("ld.shared.v2.u64 {%0, %1}, [%2+%3];" : "=l"(x), "=l"(y) : "r"(a), "n"(OFF));
+}
+
+// One vertical tap of a source word (four byte columns) into four output rows:
+// acc[2r], acc[2r+1] hold row r's byte pairs (0,1) and (2,3).  The tap is
+// entry E past the table pointers: {row address, funnel shift} at up, the
+// weight pairs (w0,w0,w1,w1),(w2,w2,w3,w3) at wp.
+template <bool SHIFT, int E>
+__device__ __forceinline__ void vertical_tap(unsigned up, unsigned wp, unsigned g4, f32x2 minus_two23, f32x2 (&acc)[8]) {
+  uint32_t ra, sh;
+  lds_v2u32<8 * E>(up, ra, sh);
+  f32x2 w0, w1, w2, w3;
+  lds_v2u64<32 * E>(wp, w0, w1);
+  lds_v2u64<32 * E + 16>(wp, w2, w3);
+  ra += g4;
+  uint32_t word = lds_u32<0>(ra);
+  if (SHIFT) {
+    word = __funnelshift_r(word, lds_u32<4>(ra), sh);
+  }
+  const f32x2 va = bytes_to_f32x2<0, 1>(word, minus_two23);
+  const f32x2 vb = bytes_to_f32x2<2, 3>(word, minus_two23);
+  ffma2(acc[0], va, w0);
+  ffma2(acc[1], vb, w0);
+  ffma2(acc[2], va, w1);
+  ffma2(acc[3], vb, w1);
+  ffma2(acc[4], va, w2);
+  ffma2(acc[5], vb, w2);
+  ffma2(acc[6], va, w3);
+  ffma2(acc[7], vb, w3);
+}
+
+// All taps of a group, two per trip: the tables are padded to an even count
+// with zero-weight entries, which leave the sums unchanged.
+template <bool SHIFT>
+__device__ __forceinline__ void vertical_taps(unsigned up, unsigned wp, unsigned g4, int cnt, f32x2 (&acc)[8]) {
+  const f32x2 minus_two23 = pack2(-8388608.0f, -8388608.0f);
+  const unsigned up_end = up + 8u * (unsigned)((cnt + 1) & ~1);
+  while (up != up_end) {
+    vertical_tap<SHIFT, 0>(up, wp, g4, minus_two23, acc);
+    vertical_tap<SHIFT, 1>(up, wp, g4, minus_two23, acc);
+    up += 16;
+    wp += 64;
+  }
+}
+
+// One output pixel's C floats; four-channel pixels go out as one 16-byte store
+// when the destination allows it.
+template <int C>
+__device__ __forceinline__ void store_pixel(float* dst, const float (&v)[C], bool vec_ok) {
+  if (C == 4 && vec_ok) {
+    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1 % C], v[2 % C], v[3 % C]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < C; c++) {
+      dst[c] = v[c];
+    }
+  }
+}
+
 // Tables that change from pass to pass (a pass = one run of output columns of
 // the band); two sets, so the next pass's tables are built while the current
 // pass is still filtering horizontally.
@@ -114,7 +200,7 @@ struct PassTables {
   int* hfirst;      // [kTileW]
   int* hcount;      // [kTileW]
   float* wh;        // [kTileW][cap_x]
-  int2* urow;       // [4][u_cap]  {word index of the staged row, funnel shift in bits}
+  int2* urow;       // [4][u_cap]  {shared address of the staged row's first word, funnel shift in bits}
 };
 
 struct Smem {
@@ -241,12 +327,13 @@ __device__ __forceinline__ void start_pass(
   for (int i = tid; i < ngroups * p.u_cap; i += kThreads) {
     const int rg = i / p.u_cap;
     const int e = i - rg * p.u_cap;
-    if (e < sm.ucount[rg]) {
+    if (e < ((sm.ucount[rg] + 1) & ~1)) {
       int lo, hi;
       axis_range(ay, by + rg * 4, lo, hi);
-      const int sr = clampi(lo + e, 0, s.pre_h - 1) - rlo;
+      const int sr = min(clampi(lo + e, 0, s.pre_h - 1) - rlo, rows - 1);
       const int phase = (int)((reinterpret_cast<uintptr_t>(g.g0) + (size_t)sr * src_pitch) & 15);
-      tab.urow[i] = make_int2((sr * g.pitch_s + phase - g.common) >> 2, ((phase - g.common) & 3) * 8);
+      const int boff = sr * g.pitch_s + phase - g.common;
+      tab.urow[i] = make_int2((int)(smem_addr(sm.srct) + (unsigned)(boff & ~3)), (boff & 3) * 8);
     }
   }
 }
@@ -303,12 +390,13 @@ __device__ void resize_rows(
       }
       sm.ucount[rg] = cnt;
     }
-    if (u <= ulast) {
+    {
+      // entries past the union get zero weights: the tap loop runs two at a time
       float w4[4];
 #pragma unroll
       for (int r = 0; r < 4; r++) {
         float w = 0.0f;
-        if (r < on && u >= lo[r] && u <= hi[r]) {
+        if (u <= ulast && r < on && u >= lo[r] && u <= hi[r]) {
           if (ay.identity) {
             w = 1.0f;
           } else {
@@ -343,6 +431,7 @@ __device__ void resize_rows(
 
   float* base = reinterpret_cast<float*>(s.dst);
   const size_t row_stride = (size_t)s.slot_w * C;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(base) & 15) == 0;
   int it = 0;
   for (;;) {
     const PassTables tab = (it & 1) ? sm.tab[1] : sm.tab[0];
@@ -354,10 +443,13 @@ __device__ void resize_rows(
 
     // ---- vertical filter: thread = (source word, group of four output rows) -----
     {
-      const uint32_t* srcw = reinterpret_cast<const uint32_t*>(sm.srct);
       // every thread owns one source word (four byte columns) and walks the row
       // groups with a stride of two; where its columns land in the planar
-      // buffer does not depend on the group
+      // buffer does not depend on the group.  Rows start on a word boundary of
+      // the staging buffer whenever the source pitch is a multiple of four.
+      const bool shifted = (((unsigned)s.src_w * C) & 3u) != 0;
+      const unsigned urow_base = smem_addr(tab.urow);
+      const unsigned uw_base = smem_addr(sm.uw);
       for (int g = tid & 127; g < cur.nwords; g += 128) {
         int off0, off1, off2, off3;
         {
@@ -373,32 +465,21 @@ __device__ void resize_rows(
         }
         for (int rg = tid >> 7; rg < ngroups; rg += kThreads >> 7) {
           const int cnt = sm.ucount[rg];
-          const int2* urow = tab.urow + rg * p.u_cap;
-          const float4* uw = sm.uw + 2 * rg * p.u_cap;
-          float a00 = 0.f, a01 = 0.f, a02 = 0.f, a03 = 0.f;
-          float a10 = 0.f, a11 = 0.f, a12 = 0.f, a13 = 0.f;
-          float a20 = 0.f, a21 = 0.f, a22 = 0.f, a23 = 0.f;
-          float a30 = 0.f, a31 = 0.f, a32 = 0.f, a33 = 0.f;
-          for (int e = 0; e < cnt; e++) {
-            const int2 ri = urow[e];
-            const float4 wa = uw[2 * e];       // (w0, w0, w1, w1)
-            const float4 wb = uw[2 * e + 1];   // (w2, w2, w3, w3)
-            uint32_t word = srcw[ri.x + g];
-            if (ri.y) {
-              word = __funnelshift_r(word, srcw[ri.x + g + 1], ri.y);
-            }
-            float v0, v1, v2, v3;
-            bytes_to_float2<0, 1>(word, v0, v1);
-            bytes_to_float2<2, 3>(word, v2, v3);
-            ffma2(a00, a01, v0, v1, wa.x, wa.y);
-            ffma2(a02, a03, v2, v3, wa.x, wa.y);
-            ffma2(a10, a11, v0, v1, wa.z, wa.w);
-            ffma2(a12, a13, v2, v3, wa.z, wa.w);
-            ffma2(a20, a21, v0, v1, wb.x, wb.y);
-            ffma2(a22, a23, v2, v3, wb.x, wb.y);
-            ffma2(a30, a31, v0, v1, wb.z, wb.w);
-            ffma2(a32, a33, v2, v3, wb.z, wb.w);
+          f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          if (shifted) {
+            vertical_taps<true>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
+          } else {
+            vertical_taps<false>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
           }
+          float a00, a01, a02, a03, a10, a11, a12, a13, a20, a21, a22, a23, a30, a31, a32, a33;
+          unpack2(acc[0], a00, a01);
+          unpack2(acc[1], a02, a03);
+          unpack2(acc[2], a10, a11);
+          unpack2(acc[3], a12, a13);
+          unpack2(acc[4], a20, a21);
+          unpack2(acc[5], a22, a23);
+          unpack2(acc[6], a30, a31);
+          unpack2(acc[7], a32, a33);
           // planar store: column (px, ch) of group rg -> mid[(rg * C + ch) * ncols + px]
           float4* plane = sm.mid + rg * C * cur.ncols;
           if (off0 >= 0) plane[off0] = make_float4(a00, a10, a20, a30);
@@ -426,39 +507,59 @@ __device__ void resize_rows(
       start_pass<C>(s, p, sm, tab_next, nxt, ay, ax, by, nr, rlo, rows);
     }
 
-    // ---- horizontal filter: thread = (output column, channel, group of four rows) ----
+    // ---- horizontal filter: thread = (output column, group of four rows), all channels ----
     {
-      const int per_rg = cur.nc * C;
-      for (int item = tid; item < ngroups * per_rg; item += kThreads) {
-        int rg, rem;
+      const unsigned plane = (unsigned)cur.ncols * 16u;
+      for (int item = tid; item < ngroups * cur.nc; item += kThreads) {
+        int rg, x;
         if (cur.nc == kTileW) {
-          rg = item / (kTileW * C);
-          rem = item - rg * (kTileW * C);
+          rg = item / kTileW;
+          x = item - rg * kTileW;
         } else {
-          rg = item / per_rg;
-          rem = item - rg * per_rg;
+          rg = item / cur.nc;
+          x = item - rg * cur.nc;
         }
-        const int x = rem / C;
-        const int ch = rem - x * C;
         const int f = tab.hfirst[x];
         const int cnt = tab.hcount[x];
-        const float2* w = reinterpret_cast<const float2*>(tab.wh) + x * s.cap_x;
-        const float4* col = sm.mid + (rg * C + ch) * cur.ncols;
-        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        unsigned wq = smem_addr(tab.wh) + (unsigned)(x * s.cap_x) * 8u;
+        const unsigned wq_end = wq + 8u * (unsigned)cnt;
+        const unsigned col_a = smem_addr(sm.mid) + (unsigned)(rg * C) * plane;
+        f32x2 acc[C][2];   // per channel: rows 0,1 and rows 2,3 of the group
+#pragma unroll
+        for (int c = 0; c < C; c++) {
+          acc[c][0] = 0;
+          acc[c][1] = 0;
+        }
         if (!cur.edge_x) {
-          const float4* c0 = col + (f - cur.clo);
-          for (int k = 0; k < cnt; k++) {
-            const float4 v = c0[k];
-            const float2 wk = w[k];
-            ffma2(a0, a1, v.x, v.y, wk.x, wk.y);
-            ffma2(a2, a3, v.z, v.w, wk.x, wk.y);
+          unsigned cp[C];
+#pragma unroll
+          for (int c = 0; c < C; c++) {
+            cp[c] = col_a + (unsigned)(f - cur.clo) * 16u + (unsigned)c * plane;
+          }
+          while (wq != wq_end) {
+            const f32x2 wk = lds_u64<0>(wq);
+#pragma unroll
+            for (int c = 0; c < C; c++) {
+              f32x2 v01, v23;
+              lds_v2u64<0>(cp[c], v01, v23);
+              ffma2(acc[c][0], v01, wk);
+              ffma2(acc[c][1], v23, wk);
+              cp[c] += 16;
+            }
+            wq += 8;
           }
         } else {
-          for (int k = 0; k < cnt; k++) {
-            const float4 v = col[clampi(f + k, 0, s.pre_w - 1) - cur.clo];
-            const float2 wk = w[k];
-            ffma2(a0, a1, v.x, v.y, wk.x, wk.y);
-            ffma2(a2, a3, v.z, v.w, wk.x, wk.y);
+          for (int k = 0; wq != wq_end; k++) {
+            const f32x2 wk = lds_u64<0>(wq);
+            const unsigned ca = col_a + (unsigned)(clampi(f + k, 0, s.pre_w - 1) - cur.clo) * 16u;
+#pragma unroll
+            for (int c = 0; c < C; c++) {
+              f32x2 v01, v23;
+              lds_v2u64<0>(ca + (unsigned)c * plane, v01, v23);
+              ffma2(acc[c][0], v01, wk);
+              ffma2(acc[c][1], v23, wk);
+            }
+            wq += 8;
           }
         }
         int px = cur.bx + x - s.post_x;
@@ -466,13 +567,26 @@ __device__ void resize_rows(
           px = s.post_w - 1 - px;
         }
         const int oy = by + rg * 4 - s.post_y;
-        const float* lut = sm.lut + ch * 256;
-        float* dst = base + ((size_t)oy * s.slot_w + px) * C + ch;
+        float* dst = base + ((size_t)oy * s.slot_w + px) * C;
         const int left = nr - rg * 4;
-        dst[0] = lut[quantise_sat(a0)];
-        if (left > 1) dst[row_stride] = lut[quantise_sat(a1)];
-        if (left > 2) dst[2 * row_stride] = lut[quantise_sat(a2)];
-        if (left > 3) dst[3 * row_stride] = lut[quantise_sat(a3)];
+        float out[4][C];
+#pragma unroll
+        for (int c = 0; c < C; c++) {
+          float a0, a1, a2, a3;
+          unpack2(acc[c][0], a0, a1);
+          unpack2(acc[c][1], a2, a3);
+          const float* lut = sm.lut + c * 256;
+          out[0][c] = lut[quantise_sat(a0)];
+          out[1][c] = lut[quantise_sat(a1)];
+          out[2][c] = lut[quantise_sat(a2)];
+          out[3][c] = lut[quantise_sat(a3)];
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+          if (r < left) {
+            store_pixel<C>(dst + r * row_stride, out[r], vec_ok);
+          }
+        }
       }
     }
     if (!more) {
@@ -649,6 +763,7 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
     configured_device = dev;
   }
   LaunchParams p = p_in;
+  p.u_cap = (p.u_cap + 1) & ~1;   // room for the zero-weight entry that makes a tap count even
   // Tiles per CTA along a row band: as many as keeps about eight waves of CTAs
   // on the device (3 CTAs per SM), at most 8.
   const long long tiles = (long long)p.n * p.tiles_y * p.tiles_x;
