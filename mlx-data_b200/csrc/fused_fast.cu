@@ -165,17 +165,15 @@ __device__ __forceinline__ void vertical_tap(unsigned up, unsigned wp, unsigned 
   ffma2(acc[7], vb, w3);
 }
 
-// All taps of a group, two per trip: the tables are padded to an even count
-// with zero-weight entries, which leave the sums unchanged.
+// All taps of a group, one per trip (unrolling by hand made the loop longer).
 template <bool SHIFT>
 __device__ __forceinline__ void vertical_taps(unsigned up, unsigned wp, unsigned g4, int cnt, f32x2 (&acc)[8]) {
   const f32x2 minus_two23 = pack2(-8388608.0f, -8388608.0f);
-  const unsigned up_end = up + 8u * (unsigned)((cnt + 1) & ~1);
+  const unsigned up_end = up + 8u * (unsigned)cnt;
   while (up != up_end) {
     vertical_tap<SHIFT, 0>(up, wp, g4, minus_two23, acc);
-    vertical_tap<SHIFT, 1>(up, wp, g4, minus_two23, acc);
-    up += 16;
-    wp += 64;
+    up += 8;
+    wp += 32;
   }
 }
 
@@ -327,7 +325,7 @@ __device__ __forceinline__ void start_pass(
   for (int i = tid; i < ngroups * p.u_cap; i += kThreads) {
     const int rg = i / p.u_cap;
     const int e = i - rg * p.u_cap;
-    if (e < ((sm.ucount[rg] + 1) & ~1)) {
+    if (e < sm.ucount[rg]) {
       int lo, hi;
       axis_range(ay, by + rg * 4, lo, hi);
       const int sr = min(clampi(lo + e, 0, s.pre_h - 1) - rlo, rows - 1);
@@ -390,13 +388,12 @@ __device__ void resize_rows(
       }
       sm.ucount[rg] = cnt;
     }
-    {
-      // entries past the union get zero weights: the tap loop runs two at a time
+    if (u <= ulast) {
       float w4[4];
 #pragma unroll
       for (int r = 0; r < 4; r++) {
         float w = 0.0f;
-        if (u <= ulast && r < on && u >= lo[r] && u <= hi[r]) {
+        if (r < on && u >= lo[r] && u <= hi[r]) {
           if (ay.identity) {
             w = 1.0f;
           } else {
@@ -443,27 +440,61 @@ __device__ void resize_rows(
 
     // ---- vertical filter: thread = (source word, group of four output rows) -----
     {
-      // every thread owns one source word (four byte columns) and walks the row
-      // groups with a stride of two; where its columns land in the planar
-      // buffer does not depend on the group.  Rows start on a word boundary of
-      // the staging buffer whenever the source pitch is a multiple of four.
+      // Rows start on a word boundary of the staging buffer whenever the source
+      // pitch is a multiple of four.
       const bool shifted = (((unsigned)s.src_w * C) & 3u) != 0;
       const unsigned urow_base = smem_addr(tab.urow);
       const unsigned uw_base = smem_addr(sm.uw);
-      for (int g = tid & 127; g < cur.nwords; g += 128) {
-        int off0, off1, off2, off3;
-        {
-          const int jb = 4 * g - cur.common;
-          int j = jb;
-          off0 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
-          j = jb + 1;
-          off1 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
-          j = jb + 2;
-          off2 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
-          j = jb + 3;
-          off3 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
+      const int nw = cur.nwords;
+      // Two ways to deal the (row group, source word) pairs out.  Blocked: a
+      // half of the CTA per group, 128 words per round - every warp works on
+      // one group, so its table loads are broadcasts and the store offsets are
+      // shared by the groups.  Flat: one sequence over all pairs, which keeps
+      // the warps full when the word count is far from a multiple of 128.
+      const int blocked_slots = ((nw + 127) >> 7) * 128 * ((ngroups + 1) >> 1) * 2;
+      if (4 * nw * ngroups >= 3 * blocked_slots) {
+        for (int g = tid & 127; g < nw; g += 128) {
+          int off0, off1, off2, off3;
+          {
+            const int jb = 4 * g - cur.common;
+            int j = jb;
+            off0 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
+            j = jb + 1;
+            off1 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
+            j = jb + 2;
+            off2 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
+            j = jb + 3;
+            off3 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
+          }
+          for (int rg = tid >> 7; rg < ngroups; rg += kThreads >> 7) {
+            const int cnt = sm.ucount[rg];
+            f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (shifted) {
+              vertical_taps<true>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
+            } else {
+              vertical_taps<false>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
+            }
+            float a00, a01, a02, a03, a10, a11, a12, a13, a20, a21, a22, a23, a30, a31, a32, a33;
+            unpack2(acc[0], a00, a01);
+            unpack2(acc[1], a02, a03);
+            unpack2(acc[2], a10, a11);
+            unpack2(acc[3], a12, a13);
+            unpack2(acc[4], a20, a21);
+            unpack2(acc[5], a22, a23);
+            unpack2(acc[6], a30, a31);
+            unpack2(acc[7], a32, a33);
+            // planar store: column (px, ch) of group rg -> mid[(rg * C + ch) * ncols + px]
+            float4* plane = sm.mid + rg * C * cur.ncols;
+            if (off0 >= 0) plane[off0] = make_float4(a00, a10, a20, a30);
+            if (off1 >= 0) plane[off1] = make_float4(a01, a11, a21, a31);
+            if (off2 >= 0) plane[off2] = make_float4(a02, a12, a22, a32);
+            if (off3 >= 0) plane[off3] = make_float4(a03, a13, a23, a33);
+          }
         }
-        for (int rg = tid >> 7; rg < ngroups; rg += kThreads >> 7) {
+      } else {
+        for (int i = tid; i < nw * ngroups; i += kThreads) {
+          const int rg = (i >= nw ? 1 : 0) + (i >= 2 * nw ? 1 : 0) + (i >= 3 * nw ? 1 : 0);
+          const int g = i - rg * nw;
           const int cnt = sm.ucount[rg];
           f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
           if (shifted) {
@@ -471,21 +502,37 @@ __device__ void resize_rows(
           } else {
             vertical_taps<false>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
           }
-          float a00, a01, a02, a03, a10, a11, a12, a13, a20, a21, a22, a23, a30, a31, a32, a33;
-          unpack2(acc[0], a00, a01);
-          unpack2(acc[1], a02, a03);
-          unpack2(acc[2], a10, a11);
-          unpack2(acc[3], a12, a13);
-          unpack2(acc[4], a20, a21);
-          unpack2(acc[5], a22, a23);
-          unpack2(acc[6], a30, a31);
-          unpack2(acc[7], a32, a33);
-          // planar store: column (px, ch) of group rg -> mid[(rg * C + ch) * ncols + px]
+          // planar store: byte column j = (px, ch) of group rg -> mid[(rg * C + ch) * ncols + px];
+          // quotient and remainder by C advance with j
           float4* plane = sm.mid + rg * C * cur.ncols;
-          if (off0 >= 0) plane[off0] = make_float4(a00, a10, a20, a30);
-          if (off1 >= 0) plane[off1] = make_float4(a01, a11, a21, a31);
-          if (off2 >= 0) plane[off2] = make_float4(a02, a12, a22, a32);
-          if (off3 >= 0) plane[off3] = make_float4(a03, a13, a23, a33);
+          const int j0 = 4 * g - cur.common;
+          int q = (j0 + 4 * C) / C - 4;
+          int r = (j0 + 4 * C) - (q + 4) * C;
+  #pragma unroll
+          for (int k = 0; k < 2; k++) {
+            float lo0, hi0, lo1, hi1, lo2, hi2, lo3, hi3;
+            unpack2(acc[0 + k], lo0, hi0);
+            unpack2(acc[2 + k], lo1, hi1);
+            unpack2(acc[4 + k], lo2, hi2);
+            unpack2(acc[6 + k], lo3, hi3);
+            const int j = j0 + 2 * k;
+            if (j >= 0 && j < cur.wbytes) {
+              plane[r * cur.ncols + q] = make_float4(lo0, lo1, lo2, lo3);
+            }
+            r++;
+            if (r == C) {
+              r = 0;
+              q++;
+            }
+            if (j + 1 >= 0 && j + 1 < cur.wbytes) {
+              plane[r * cur.ncols + q] = make_float4(hi0, hi1, hi2, hi3);
+            }
+            r++;
+            if (r == C) {
+              r = 0;
+              q++;
+            }
+          }
         }
       }
     }
@@ -763,7 +810,6 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
     configured_device = dev;
   }
   LaunchParams p = p_in;
-  p.u_cap = (p.u_cap + 1) & ~1;   // room for the zero-weight entry that makes a tap count even
   // Tiles per CTA along a row band: as many as keeps about eight waves of CTAs
   // on the device (3 CTAs per SM), at most 8.
   const long long tiles = (long long)p.n * p.tiles_y * p.tiles_x;
