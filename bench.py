@@ -23,6 +23,10 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused_fast_kernel launch per
+# image of the workload, from an ncu capture of a 128-image launch (851.3 MB);
+# the traffic of this kernel grows in proportion to the image count.
+NCU_DRAM_BYTES_PER_IMAGE = {"c5": 851.3e6 / 128}
 
 
 def load_package():
@@ -417,7 +421,8 @@ def main():
                          "frac": achieved / peak, "peak_kind": peak_kind,
                          "frac_of_nominal_8tbs": achieved / NOMINAL_HBM_GBS,
                          "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": algo_per_launch,
-                         "traffic": None},
+                         "traffic": (NCU_DRAM_BYTES_PER_IMAGE[name] * batch if name in NCU_DRAM_BYTES_PER_IMAGE else None),
+                         "traffic_kind": "ncu dram bytes of a 128-image launch scaled by the image count"},
             "cpu_baseline": cpu,
         }
         print(json.dumps(line), flush=True)
