@@ -25,25 +25,22 @@ __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
-               : "memory");
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile(
-      "{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_addr(bar))
-      : "memory");
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
 }
 
 // Bounded wait for the phase with the given parity.  Returns false when the
 // limit was reached; the caller records that and goes on without hanging.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
-  const uint32_t a = smem_addr(bar);
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+  const uint32_t a = bar;
   for (unsigned i = 0; i < kSpinLimit; i++) {
     unsigned done;
     asm volatile(
@@ -59,12 +56,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
 }
 
 // 16-byte aligned global -> shared bulk copy, bytes a multiple of 16.
-__device__ __forceinline__ void bulk_copy(void* dst_smem, const void* src_gmem, unsigned bytes, uint64_t* bar) {
+__device__ __forceinline__ void bulk_copy(unsigned dst_smem, const void* src_gmem, unsigned bytes, unsigned bar) {
   asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-          smem_addr(dst_smem)),
-      "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar))
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+      "l"(src_gmem), "r"(bytes), "r"(bar)
       : "memory");
+}
+
+// Typed view of a shared-space address.
+template <typename T>
+__device__ __forceinline__ T* sp(unsigned a) {
+  return reinterpret_cast<T*>(__cvta_shared_to_generic(a));
 }
 
 __device__ __forceinline__ void fence_async_smem() {
@@ -191,54 +193,54 @@ __device__ __forceinline__ void store_pixel(float* dst, const float (&v)[C], boo
   }
 }
 
-// Tables that change from pass to pass (a pass = one run of output columns of
-// the band); two sets, so the next pass's tables are built while the current
-// pass is still filtering horizontally.
-struct PassTables {
-  int* hfirst;      // [kTileW]
-  int* hcount;      // [kTileW]
-  float* wh;        // [kTileW][cap_x]
-  int2* urow;       // [4][u_cap]  {shared address of the staged row's first word, funnel shift in bits}
+// Shared memory of a CTA, as shared-space byte addresses (32-bit: a struct of
+// generic pointers would hold twice the registers across the pass loop).
+// There are two sets of the tables that change from pass to pass (a pass = one
+// run of output columns of the band), so the next pass's are built while the
+// current pass is still filtering horizontally.  One set:
+//   +0              int   hfirst[kTileW]
+//   +256            int   hcount[kTileW]
+//   +512            int2  urow[4][u_cap]  {shared address of the staged row's first word, funnel shift in bits}
+//   +wh_off         float2 wh[kTileW][cap_x]  (w, w) pairs
+struct Smem {
+  unsigned lut;         // float [c][256]
+  unsigned tab0;        // first table set
+  unsigned tab_stride;  // bytes from one set to the next
+  unsigned wh_off;
+  unsigned uw;          // float4 [4][u_cap][2]  weight of a union row in each of the group's four outputs
+  unsigned ucount;      // int [4]
+  unsigned bar;
+  unsigned mid;         // float4 [4][C][ncols]
+  unsigned srct;
 };
 
-struct Smem {
-  float* lut;       // [c][256]
-  PassTables tab[2];
-  float4* uw;       // [4][u_cap]  weight of a union row in each of the group's four outputs
-  int* ucount;      // [4]
-  uint64_t* bar;
-  float4* mid;      // [4][C][ncols]
-  uint8_t* srct;
-};
+constexpr unsigned kTabHcount = kTileW * 4;
+constexpr unsigned kTabUrow = kTileW * 8;
 
 __host__ __device__ inline size_t align16(size_t v) {
   return (v + 15) & ~(size_t)15;
 }
 
-__host__ __device__ inline size_t smem_layout(const LaunchParams& p, unsigned char* base, Smem* out) {
+// Fills `out` with addresses relative to `base` (the shared-space address of
+// the dynamic shared memory) and returns the bytes needed.
+__host__ __device__ inline size_t smem_layout(const LaunchParams& p, unsigned base, Smem* out) {
   Smem sm;
   size_t off = 0;
-  sm.lut = reinterpret_cast<float*>(base + off);
+  sm.lut = base + (unsigned)off;
   off += (size_t)p.c_out * 256 * sizeof(float);
-  for (int k = 0; k < 2; k++) {
-    sm.tab[k].hfirst = reinterpret_cast<int*>(base + off);
-    off += kTileW * sizeof(int);
-    sm.tab[k].hcount = reinterpret_cast<int*>(base + off);
-    off += kTileW * sizeof(int);
-    sm.tab[k].urow = reinterpret_cast<int2*>(base + off);
-    off += (size_t)4 * p.u_cap * sizeof(int2);
-    sm.tab[k].wh = reinterpret_cast<float*>(base + off);   // (w, w) pairs
-    off = align16(off + (size_t)p.weight_floats * 2 * sizeof(float));
-  }
-  sm.uw = reinterpret_cast<float4*>(base + off);
+  sm.tab0 = base + (unsigned)off;
+  sm.wh_off = (unsigned)align16(kTabUrow + (size_t)4 * p.u_cap * sizeof(int2));
+  sm.tab_stride = (unsigned)align16(sm.wh_off + (size_t)p.weight_floats * 2 * sizeof(float));
+  off += 2 * (size_t)sm.tab_stride;
+  sm.uw = base + (unsigned)off;
   off += (size_t)4 * p.u_cap * 2 * sizeof(float4);
-  sm.ucount = reinterpret_cast<int*>(base + off);
+  sm.ucount = base + (unsigned)off;
   off += 16;
-  sm.bar = reinterpret_cast<uint64_t*>(base + off);
+  sm.bar = base + (unsigned)off;
   off += 16;
-  sm.mid = reinterpret_cast<float4*>(base + off);
+  sm.mid = base + (unsigned)off;
   off = align16(off + (size_t)p.mid_float4s * 16);
-  sm.srct = base + off;
+  sm.srct = base + (unsigned)off;
   off += (size_t)p.src_tile_bytes;
   if (out) {
     *out = sm;
@@ -280,7 +282,7 @@ __device__ __forceinline__ PassGeom pass_geom(const DevSample& s, const Axis& ax
 // the vertical union).
 template <int C>
 __device__ __forceinline__ void start_pass(
-    const DevSample& s, const LaunchParams& p, const Smem& sm, const PassTables& tab, const PassGeom& g,
+    const DevSample& s, const LaunchParams& p, const Smem& sm, unsigned tab, const PassGeom& g,
     const Axis& ay, const Axis& ax, int by, int nr, int rlo, int rows) {
   const int tid = threadIdx.x;
   const size_t src_pitch = (size_t)s.src_w * C;
@@ -289,7 +291,7 @@ __device__ __forceinline__ void start_pass(
     const int phase = (int)(ga & 15);
     const unsigned len = (unsigned)((phase + g.wbytes + 15) & ~15);
     mbar_expect_tx(sm.bar, len);
-    bulk_copy(sm.srct + tid * g.pitch_s, reinterpret_cast<const void*>(ga - phase), len, sm.bar);
+    bulk_copy(sm.srct + (unsigned)(tid * g.pitch_s), reinterpret_cast<const void*>(ga - phase), len, sm.bar);
   }
   // horizontal taps: one thread per output column (the last warps, which issue
   // no copies); every weight is stored twice, side by side, so the packed
@@ -301,9 +303,9 @@ __device__ __forceinline__ void start_pass(
       axis_range(ax, g.bx + x, lo, hi);
       int cnt = hi - lo + 1;
       cnt = cnt > s.cap_x ? s.cap_x : cnt;
-      tab.hfirst[x] = lo;
-      tab.hcount[x] = cnt;
-      float2* w2 = reinterpret_cast<float2*>(tab.wh) + x * s.cap_x;
+      sp<int>(tab)[x] = lo;
+      sp<int>(tab + kTabHcount)[x] = cnt;
+      float2* w2 = sp<float2>(tab + sm.wh_off) + x * s.cap_x;
       if (ax.identity) {
         w2[0] = make_float2(1.0f, 1.0f);
       } else {
@@ -325,13 +327,13 @@ __device__ __forceinline__ void start_pass(
   for (int i = tid; i < ngroups * p.u_cap; i += kThreads) {
     const int rg = i / p.u_cap;
     const int e = i - rg * p.u_cap;
-    if (e < sm.ucount[rg]) {
+    if (e < sp<int>(sm.ucount)[rg]) {
       int lo, hi;
       axis_range(ay, by + rg * 4, lo, hi);
       const int sr = min(clampi(lo + e, 0, s.pre_h - 1) - rlo, rows - 1);
       const int phase = (int)((reinterpret_cast<uintptr_t>(g.g0) + (size_t)sr * src_pitch) & 15);
       const int boff = sr * g.pitch_s + phase - g.common;
-      tab.urow[i] = make_int2((int)(smem_addr(sm.srct) + (unsigned)(boff & ~3)), (boff & 3) * 8);
+      sp<int2>(tab + kTabUrow)[i] = make_int2((int)(sm.srct + (unsigned)(boff & ~3)), (boff & 3) * 8);
     }
   }
 }
@@ -386,7 +388,7 @@ __device__ void resize_rows(
         cnt = p.u_cap;
         atomicOr(p.status, 8);
       }
-      sm.ucount[rg] = cnt;
+      sp<int>(sm.ucount)[rg] = cnt;
     }
     if (u <= ulast) {
       float w4[4];
@@ -407,8 +409,8 @@ __device__ void resize_rows(
         }
         w4[r] = w;
       }
-      sm.uw[2 * i] = make_float4(w4[0], w4[0], w4[1], w4[1]);
-      sm.uw[2 * i + 1] = make_float4(w4[2], w4[2], w4[3], w4[3]);
+      sp<float4>(sm.uw)[2 * i] = make_float4(w4[0], w4[0], w4[1], w4[1]);
+      sp<float4>(sm.uw)[2 * i + 1] = make_float4(w4[2], w4[2], w4[3], w4[3]);
     }
   }
   __syncthreads();   // ucount is read by start_pass
@@ -420,7 +422,7 @@ __device__ void resize_rows(
     }
     return;
   }
-  start_pass<C>(s, p, sm, sm.tab[0], cur, ay, ax, by, nr, rlo, rows);
+  start_pass<C>(s, p, sm, sm.tab0, cur, ay, ax, by, nr, rlo, rows);
   __syncthreads();
   if (tid == 0) {
     mbar_arrive(sm.bar);
@@ -431,8 +433,8 @@ __device__ void resize_rows(
   const bool vec_ok = (reinterpret_cast<uintptr_t>(base) & 15) == 0;
   int it = 0;
   for (;;) {
-    const PassTables tab = (it & 1) ? sm.tab[1] : sm.tab[0];
-    const PassTables tab_next = (it & 1) ? sm.tab[0] : sm.tab[1];
+    const unsigned tab = sm.tab0 + ((it & 1) ? sm.tab_stride : 0u);
+    const unsigned tab_next = sm.tab0 + ((it & 1) ? 0u : sm.tab_stride);
     if (!mbar_wait(sm.bar, parity)) {
       atomicOr(p.status, 4);
     }
@@ -443,8 +445,8 @@ __device__ void resize_rows(
       // Rows start on a word boundary of the staging buffer whenever the source
       // pitch is a multiple of four.
       const bool shifted = (((unsigned)s.src_w * C) & 3u) != 0;
-      const unsigned urow_base = smem_addr(tab.urow);
-      const unsigned uw_base = smem_addr(sm.uw);
+      const unsigned urow_base = tab + kTabUrow;
+      const unsigned uw_base = sm.uw;
       const int nw = cur.nwords;
       // Two ways to deal the (row group, source word) pairs out.  Blocked: a
       // half of the CTA per group, 128 words per round - every warp works on
@@ -467,7 +469,7 @@ __device__ void resize_rows(
             off3 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
           }
           for (int rg = tid >> 7; rg < ngroups; rg += kThreads >> 7) {
-            const int cnt = sm.ucount[rg];
+            const int cnt = sp<int>(sm.ucount)[rg];
             f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (shifted) {
               vertical_taps<true>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
@@ -484,7 +486,7 @@ __device__ void resize_rows(
             unpack2(acc[6], a30, a31);
             unpack2(acc[7], a32, a33);
             // planar store: column (px, ch) of group rg -> mid[(rg * C + ch) * ncols + px]
-            float4* plane = sm.mid + rg * C * cur.ncols;
+            float4* plane = sp<float4>(sm.mid) + rg * C * cur.ncols;
             if (off0 >= 0) plane[off0] = make_float4(a00, a10, a20, a30);
             if (off1 >= 0) plane[off1] = make_float4(a01, a11, a21, a31);
             if (off2 >= 0) plane[off2] = make_float4(a02, a12, a22, a32);
@@ -495,7 +497,7 @@ __device__ void resize_rows(
         for (int i = tid; i < nw * ngroups; i += kThreads) {
           const int rg = (i >= nw ? 1 : 0) + (i >= 2 * nw ? 1 : 0) + (i >= 3 * nw ? 1 : 0);
           const int g = i - rg * nw;
-          const int cnt = sm.ucount[rg];
+          const int cnt = sp<int>(sm.ucount)[rg];
           f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
           if (shifted) {
             vertical_taps<true>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
@@ -504,7 +506,7 @@ __device__ void resize_rows(
           }
           // planar store: byte column j = (px, ch) of group rg -> mid[(rg * C + ch) * ncols + px];
           // quotient and remainder by C advance with j
-          float4* plane = sm.mid + rg * C * cur.ncols;
+          float4* plane = sp<float4>(sm.mid) + rg * C * cur.ncols;
           const int j0 = 4 * g - cur.common;
           int q = (j0 + 4 * C) / C - 4;
           int r = (j0 + 4 * C) - (q + 4) * C;
@@ -566,11 +568,11 @@ __device__ void resize_rows(
           rg = item / cur.nc;
           x = item - rg * cur.nc;
         }
-        const int f = tab.hfirst[x];
-        const int cnt = tab.hcount[x];
-        unsigned wq = smem_addr(tab.wh) + (unsigned)(x * s.cap_x) * 8u;
+        const int f = (int)lds_u32<0>(tab + 4u * (unsigned)x);
+        const int cnt = (int)lds_u32<kTabHcount>(tab + 4u * (unsigned)x);
+        unsigned wq = tab + sm.wh_off + (unsigned)(x * s.cap_x) * 8u;
         const unsigned wq_end = wq + 8u * (unsigned)cnt;
-        const unsigned col_a = smem_addr(sm.mid) + (unsigned)(rg * C) * plane;
+        const unsigned col_a = sm.mid + (unsigned)(rg * C) * plane;
         f32x2 acc[C][2];   // per channel: rows 0,1 and rows 2,3 of the group
 #pragma unroll
         for (int c = 0; c < C; c++) {
@@ -622,11 +624,11 @@ __device__ void resize_rows(
           float a0, a1, a2, a3;
           unpack2(acc[c][0], a0, a1);
           unpack2(acc[c][1], a2, a3);
-          const float* lut = sm.lut + c * 256;
-          out[0][c] = lut[quantise_sat(a0)];
-          out[1][c] = lut[quantise_sat(a1)];
-          out[2][c] = lut[quantise_sat(a2)];
-          out[3][c] = lut[quantise_sat(a3)];
+          const unsigned lut = sm.lut + (unsigned)c * 1024u;
+          out[0][c] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a0)));
+          out[1][c] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a1)));
+          out[2][c] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a2)));
+          out[3][c] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a3)));
         }
 #pragma unroll
         for (int r = 0; r < 4; r++) {
@@ -733,13 +735,13 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
   }
   if (s.mode == kModeResize) {
     Smem sm;
-    smem_layout(p, smem_raw, &sm);
+    smem_layout(p, smem_addr(smem_raw), &sm);
     if (threadIdx.x == 0) {
       mbar_init(sm.bar, 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = threadIdx.x; i < C * 256; i += kThreads) {
-      sm.lut[i] = __ldg(p.lut + i);
+      sp<float>(sm.lut)[i] = __ldg(p.lut + i);
     }
     __syncthreads();
     int gx_lo, gx_hi;
@@ -780,7 +782,7 @@ size_t fused_fast_smem_bytes(const LaunchParams& p) {
   if (p.src_tile_bytes == 0) {
     return 0;   // no sample resizes: nothing is staged
   }
-  return smem_layout(p, nullptr, nullptr);
+  return smem_layout(p, 0u, nullptr);
 }
 
 cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
@@ -799,7 +801,7 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
     worst.src_tile_bytes = kSrcTileBytes;
     worst.u_cap = kMaxStagedRows;
     e = cudaFuncSetAttribute(
-        fused_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_layout(worst, nullptr, nullptr));
+        fused_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_layout(worst, 0u, nullptr));
     if (e != cudaSuccess) {
       return e;
     }
