@@ -100,44 +100,64 @@ static int check_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc*
   return MLXD_OK;
 }
 
-static int plan_resize(DevSample& s, int C, int i, PassNeed& need) {
-  int sub_h = kTileH, sub_w = kTileW;
-  for (;;) {
-    const AxisPlan ay = plan_axis(s.pre_h, s.geom_h, sub_h);
-    const AxisPlan ax = plan_axis(s.pre_w, s.geom_w, sub_w);
-    bool fits = false;
-    PassNeed n = plan_pass(ay, ax, sub_h, sub_w, s.pre_h, s.pre_w, C, fits);
-    // source rows feeding one group of (at most) four adjacent output rows
-    n.u_cap = plan_axis(s.pre_h, s.geom_h, std::min(4, sub_h)).extent;
-    fits = fits && n.u_cap <= kMaxStagedRows;
-    if (fits) {
-      s.sub_h = sub_h;
-      s.sub_w = sub_w;
-      s.cap_y = ay.cap;
-      s.cap_x = ax.cap;
-      need.src_bytes = std::max(need.src_bytes, n.src_bytes);
-      need.mid_float4s = std::max(need.mid_float4s, n.mid_float4s);
-      need.weight_floats = std::max(need.weight_floats, n.weight_floats);
-      need.u_cap = std::max(need.u_cap, n.u_cap);
-      return MLXD_OK;
-    }
-    if (sub_h > 4) {
-      sub_h /= 2;
-    } else if (sub_w > 8) {
-      sub_w /= 2;
-    } else if (sub_h > 1) {
-      sub_h /= 2;
-    } else if (sub_w > 1) {
-      sub_w /= 2;
-    } else {
-      return fail(
-          MLXD_ERR_UNSUPPORTED,
-          "sample " + std::to_string(i) + ": shrink ratio too large for the on-chip filter footprint");
+// Shared memory of the float32 kernel that grows with the pass (staged source,
+// planar buffer, two table sets, vertical weights), and the budget under which
+// three CTAs still fit on one SM next to the fixed part (cast table, headers).
+static long long pass_bytes(const PassNeed& n) {
+  return (long long)n.src_bytes + 16LL * n.mid_float4s + 16LL * n.weight_floats + 256LL * n.u_cap;
+}
+constexpr long long kPassBudgetBytes = 70 * 1024;
+
+static int plan_resize(DevSample& s, int C, int i, PassNeed& need, long long pass_budget) {
+  // First look for the largest pass within the three-CTA budget, not going
+  // below 4 x 16 outputs; failing that, take the largest pass that fits at all.
+  for (int budgeted = 1; budgeted >= 0; budgeted--) {
+    int sub_h = kTileH, sub_w = kTileW;
+    for (;;) {
+      const AxisPlan ay = plan_axis(s.pre_h, s.geom_h, sub_h);
+      const AxisPlan ax = plan_axis(s.pre_w, s.geom_w, sub_w);
+      bool fits = false;
+      PassNeed n = plan_pass(ay, ax, sub_h, sub_w, s.pre_h, s.pre_w, C, fits);
+      // source rows feeding one group of (at most) four adjacent output rows
+      n.u_cap = plan_axis(s.pre_h, s.geom_h, std::min(4, sub_h)).extent;
+      fits = fits && n.u_cap <= kMaxStagedRows;
+      if (budgeted) {
+        fits = fits && pass_bytes(n) <= pass_budget;
+      }
+      if (fits) {
+        s.sub_h = sub_h;
+        s.sub_w = sub_w;
+        s.cap_y = ay.cap;
+        s.cap_x = ax.cap;
+        need.src_bytes = std::max(need.src_bytes, n.src_bytes);
+        need.mid_float4s = std::max(need.mid_float4s, n.mid_float4s);
+        need.weight_floats = std::max(need.weight_floats, n.weight_floats);
+        need.u_cap = std::max(need.u_cap, n.u_cap);
+        return MLXD_OK;
+      }
+      if (budgeted && sub_h <= 4 && sub_w <= 16) {
+        break;
+      }
+      if (sub_h > 4) {
+        sub_h /= 2;
+      } else if (sub_w > 8) {
+        sub_w /= 2;
+      } else if (sub_h > 1) {
+        sub_h /= 2;
+      } else if (sub_w > 1) {
+        sub_w /= 2;
+      } else {
+        return fail(
+            MLXD_ERR_UNSUPPORTED,
+            "sample " + std::to_string(i) + ": shrink ratio too large for the on-chip filter footprint");
+      }
     }
   }
+  return fail(MLXD_ERR_UNSUPPORTED, "sample " + std::to_string(i) + ": no pass size fits");
 }
 
-int plan_one_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, DevSample& out, PassNeed& need) {
+int plan_one_sample(
+    const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, DevSample& out, PassNeed& need, long long pass_budget) {
   {
     int rc = check_sample(d, i, b, b->slot_h, b->slot_w);
     if (rc != MLXD_OK) {
@@ -171,7 +191,7 @@ int plan_one_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, 
         s.mode = kModeCopy;  // identity on both axes
       } else {
         s.mode = kModeResize;
-        rc = plan_resize(s, b->channels, i, need);
+        rc = plan_resize(s, b->channels, i, need, pass_budget);
         if (rc != MLXD_OK) {
           return rc;
         }
@@ -195,18 +215,32 @@ int plan_one_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, 
   return MLXD_OK;
 }
 
-int plan_samples(
-    const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b,
-    std::vector<DevSample>& out, PassNeed& need) {
-  need = PassNeed{0, 0, 0, 0, 0};
-  out.resize(n);
-  for (int i = 0; i < n; i++) {
-    const int rc = plan_one_sample(samples[i], i, b, out[i], need);
-    if (rc != MLXD_OK) {
-      return rc;
+int plan_into(const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b, DevSample* out, PassNeed& need) {
+  // A launch allocates the largest need of every kind over its samples, which
+  // may come from different samples.  If the combination misses the three-CTA
+  // budget, one try with smaller passes; if that is not enough either, the
+  // full-size passes at two CTAs per SM are the better deal.
+  const long long budgets[3] = {kPassBudgetBytes, kPassBudgetBytes - 8 * 1024, kPassBudgetBytes};
+  for (int k = 0; k < 3; k++) {
+    need = PassNeed{0, 0, 0, 0, 0};
+    for (int i = 0; i < n; i++) {
+      const int rc = plan_one_sample(samples[i], i, b, out[i], need, budgets[k]);
+      if (rc != MLXD_OK) {
+        return rc;
+      }
+    }
+    if (pass_bytes(need) <= kPassBudgetBytes) {
+      break;
     }
   }
   return MLXD_OK;
+}
+
+int plan_samples(
+    const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b,
+    std::vector<DevSample>& out, PassNeed& need) {
+  out.resize(n);
+  return plan_into(samples, n, b, out.data(), need);
 }
 
 // Source samples of an n_src -> n_dst axis that outputs [o_lo, o_hi) can read,

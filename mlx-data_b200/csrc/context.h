@@ -84,7 +84,10 @@ int plan_samples(
     std::vector<DevSample>& out, PassNeed& need);
 
 // One sample of plan_samples; `need` accumulates the shared-memory bounds.
-int plan_one_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, DevSample& out, PassNeed& need);
+int plan_one_sample(
+    const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, DevSample& out, PassNeed& need, long long pass_budget);
+// plan_samples into caller-owned storage of n entries.
+int plan_into(const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b, DevSample* out, PassNeed& need);
 
 // The cast table of a batch descriptor: table[c * 256 + v], c < c_out.
 void compute_cast_table(const mlxd_batch_desc* b, int c_out, float* table);

@@ -479,7 +479,12 @@ PassNeed plan_pass(
   const long long pitch = (wbytes + 49 + 15) & ~15LL;   // covers both staging layouts
   const long long nwords = (wbytes + 6) / 4 + 1;
   const long long src = rows * pitch;
-  const long long mid4 = 16 * nwords;
+  // the float32 kernel pads every plane by up to 7 columns on either side and
+  // skips one slot after every eight columns
+  const long long pad = (7 + channels - 1) / channels;
+  const long long pslots = (cols + 2 * pad) + (cols + 2 * pad) / 8 + 1;
+  const long long mid4_fast = ((sub_h + 3) / 4) * channels * pslots;   // one set of planes per group of four rows
+  const long long mid4 = 16 * nwords > mid4_fast ? 16 * nwords : mid4_fast;
   const long long wts = (long long)sub_h * ay.cap + (long long)sub_w * ax.cap;
   fits = src <= kSrcTileBytes && mid4 * 4 <= kMidFloats && wts <= kWeightFloats && rows <= kMaxStagedRows;
   PassNeed n;

@@ -139,43 +139,135 @@ __device__ __forceinline__ void lds_v2u64(unsigned a, f32x2& x, f32x2& y) {
   asm volatile("ld.shared.v2.u64 {%0, %1}, [%2+%3];" : "=l"(x), "=l"(y) : "r"(a), "n"(OFF));
 }
 
-// One vertical tap of a source word (four byte columns) into four output rows:
-// acc[2r], acc[2r+1] hold row r's byte pairs (0,1) and (2,3).  The tap is
-// entry E past the table pointers: {row address, funnel shift} at up, the
-// weight pairs (w0,w0,w1,w1),(w2,w2,w3,w3) at wp.
-template <bool SHIFT, int E>
-__device__ __forceinline__ void vertical_tap(unsigned up, unsigned wp, unsigned g4, f32x2 minus_two23, f32x2 (&acc)[8]) {
-  uint32_t ra, sh;
-  lds_v2u32<8 * E>(up, ra, sh);
-  f32x2 w0, w1, w2, w3;
-  lds_v2u64<32 * E>(wp, w0, w1);
-  lds_v2u64<32 * E + 16>(wp, w2, w3);
-  ra += g4;
-  uint32_t word = lds_u32<0>(ra);
-  if (SHIFT) {
-    word = __funnelshift_r(word, lds_u32<4>(ra), sh);
-  }
-  const f32x2 va = bytes_to_f32x2<0, 1>(word, minus_two23);
-  const f32x2 vb = bytes_to_f32x2<2, 3>(word, minus_two23);
-  ffma2(acc[0], va, w0);
-  ffma2(acc[1], vb, w0);
-  ffma2(acc[2], va, w1);
-  ffma2(acc[3], vb, w1);
-  ffma2(acc[4], va, w2);
-  ffma2(acc[5], vb, w2);
-  ffma2(acc[6], va, w3);
-  ffma2(acc[7], vb, w3);
+template <int OFF>
+__device__ __forceinline__ void sts_v2f32(unsigned a, float x, float y) {
+  asm volatile("st.shared.v2.f32 [%0+%1], {%2, %3};" ::"r"(a), "n"(OFF), "f"(x), "f"(y) : "memory");
 }
 
-// All taps of a group, one per trip (unrolling by hand made the loop longer).
+// Columns of padding on either side of every plane of the planar buffer: an
+// octet of byte columns may start up to 7 before the first staged byte and end
+// up to 7 past the last, and its stores are not bounds-checked.
+template <int C>
+struct PlanePad {
+  static constexpr int value = (7 + C - 1) / C;
+};
+
+// Slot of column c (>= 0, padding included) inside its plane: one slot is
+// skipped after every eight columns.  Threads of a warp touch columns a fixed
+// distance apart - 8/C columns per lane in the vertical pass, the resize ratio
+// in the horizontal one - and with 16-byte slots in a row every distance that
+// is a multiple of 2 would keep hitting the same banks.
+__device__ __forceinline__ int skew(int c) {
+  return c + (c >> 3);
+}
+
+// Slots per plane for ncols staged columns.
+template <int C>
+__device__ __forceinline__ int plane_slots(int ncols) {
+  return skew(ncols + 2 * PlanePad<C>::value) + 1;
+}
+
+// The eight results of one thread of the vertical pass - byte columns j0..j0+7
+// of a row pair - go to the planar buffer: byte column j = (px, ch) sits in
+// plane ch at slot skew(pad + px).  b[m] is the shared address of column
+// j0 + m for m < C and low[m] that column's index modulo 8; column j0 + k =
+// j0 + m + C * t is t columns further in the same plane, one slot more when
+// it crosses a multiple of eight.  Columns outside the staged row land in the
+// padding.
+template <int C, int K>
+__device__ __forceinline__ void store_column(const unsigned (&b)[C], const int (&low)[C], float x, float y) {
+  constexpr int m = K % C;
+  constexpr int t = K / C;
+  if (t == 0) {
+    sts_v2f32<0>(b[m], x, y);
+  } else {
+    // t <= 7: at most one multiple of eight is crossed
+    const unsigned a = b[m] + ((low[m] + t) >= 8 ? 16u : 0u);
+    sts_v2f32<16 * t>(a, x, y);
+  }
+}
+
+template <int C>
+__device__ __forceinline__ void store_octet(const unsigned (&b)[C], const int (&low)[C], const f32x2 (&acc)[8]) {
+  float lo0, hi0, lo1, hi1;
+  unpack2(acc[0], lo0, hi0);
+  unpack2(acc[2], lo1, hi1);
+  store_column<C, 0>(b, low, lo0, lo1);
+  store_column<C, 1>(b, low, hi0, hi1);
+  unpack2(acc[1], lo0, hi0);
+  unpack2(acc[3], lo1, hi1);
+  store_column<C, 2>(b, low, lo0, lo1);
+  store_column<C, 3>(b, low, hi0, hi1);
+  unpack2(acc[4], lo0, hi0);
+  unpack2(acc[6], lo1, hi1);
+  store_column<C, 4>(b, low, lo0, lo1);
+  store_column<C, 5>(b, low, hi0, hi1);
+  unpack2(acc[5], lo0, hi0);
+  unpack2(acc[7], lo1, hi1);
+  store_column<C, 6>(b, low, lo0, lo1);
+  store_column<C, 7>(b, low, hi0, hi1);
+}
+
+// Byte offsets and low bits (see store_octet) of the octet that starts at byte
+// column j0, relative to the first plane of a group; pslots = slots per plane.
+template <int C>
+__device__ __forceinline__ void octet_offsets(int j0, int pslots, unsigned (&b)[C], int (&low)[C]) {
+  const int q0 = (j0 + 8 * C) / C - 8;
+  const int r0 = (j0 + 8 * C) - (q0 + 8) * C;
+#pragma unroll
+  for (int m = 0; m < C; m++) {
+    const int r = r0 + m;
+    const int wrap = r >= C ? 1 : 0;
+    const int c = PlanePad<C>::value + q0 + wrap;
+    low[m] = c & 7;
+    b[m] = (unsigned)(((r - wrap * C) * pslots + skew(c)) * 16);
+  }
+}
+
+// Vertical taps of eight adjacent byte columns (two source words) into a pair
+// of output rows.  acc[4 * h + 2 * r + k] holds, for word h and row r of the
+// pair, the byte pair (2k, 2k+1).  up walks the {row address, funnel shift}
+// table of the pair's union of source rows, wp its weights (w0,w0,w1,w1); g8 is
+// the thread's byte offset in every staged row.  Without SHIFT every staged
+// row starts on an 8-byte boundary and the two words come with one load.
 template <bool SHIFT>
-__device__ __forceinline__ void vertical_taps(unsigned up, unsigned wp, unsigned g4, int cnt, f32x2 (&acc)[8]) {
+__device__ __forceinline__ void vertical_taps(unsigned up, unsigned wp, unsigned g8, int cnt, f32x2 (&acc)[8]) {
   const f32x2 minus_two23 = pack2(-8388608.0f, -8388608.0f);
   const unsigned up_end = up + 8u * (unsigned)cnt;
   while (up != up_end) {
-    vertical_tap<SHIFT, 0>(up, wp, g4, minus_two23, acc);
+    uint32_t ra, sh;
+    lds_v2u32<0>(up, ra, sh);
+    f32x2 w0, w1;
+    lds_v2u64<0>(wp, w0, w1);
+    ra += g8;
+    uint32_t wa, wb;
+    if (SHIFT) {
+      const uint32_t x0 = lds_u32<0>(ra);
+      const uint32_t x1 = lds_u32<4>(ra);
+      const uint32_t x2 = lds_u32<8>(ra);
+      wa = __funnelshift_r(x0, x1, sh);
+      wb = __funnelshift_r(x1, x2, sh);
+    } else {
+      lds_v2u32<0>(ra, wa, wb);
+    }
+    {
+      const f32x2 va = bytes_to_f32x2<0, 1>(wa, minus_two23);
+      const f32x2 vb = bytes_to_f32x2<2, 3>(wa, minus_two23);
+      ffma2(acc[0], va, w0);
+      ffma2(acc[1], vb, w0);
+      ffma2(acc[2], va, w1);
+      ffma2(acc[3], vb, w1);
+    }
+    {
+      const f32x2 va = bytes_to_f32x2<0, 1>(wb, minus_two23);
+      const f32x2 vb = bytes_to_f32x2<2, 3>(wb, minus_two23);
+      ffma2(acc[4], va, w0);
+      ffma2(acc[5], vb, w0);
+      ffma2(acc[6], va, w1);
+      ffma2(acc[7], vb, w1);
+    }
     up += 8;
-    wp += 32;
+    wp += 16;
   }
 }
 
@@ -200,17 +292,17 @@ __device__ __forceinline__ void store_pixel(float* dst, const float (&v)[C], boo
 // current pass is still filtering horizontally.  One set:
 //   +0              int   hfirst[kTileW]
 //   +256            int   hcount[kTileW]
-//   +512            int2  urow[4][u_cap]  {shared address of the staged row's first word, funnel shift in bits}
+//   +512            int2  urow[8][u_cap]  {shared address of the staged row's first word, funnel shift in bits}
 //   +wh_off         float2 wh[kTileW][cap_x]  (w, w) pairs
 struct Smem {
   unsigned lut;         // float [c][256]
   unsigned tab0;        // first table set
   unsigned tab_stride;  // bytes from one set to the next
   unsigned wh_off;
-  unsigned uw;          // float4 [4][u_cap][2]  weight of a union row in each of the group's four outputs
-  unsigned ucount;      // int [4]
+  unsigned uw;          // float4 [8][u_cap]  (w0,w0,w1,w1): weight of a union row in the two outputs of a row pair
+  unsigned ucount;      // int [8]  rows in each row pair's union
   unsigned bar;
-  unsigned mid;         // float4 [4][C][ncols]
+  unsigned mid;         // float4 [4][C][plane_slots]
   unsigned srct;
 };
 
@@ -229,13 +321,13 @@ __host__ __device__ inline size_t smem_layout(const LaunchParams& p, unsigned ba
   sm.lut = base + (unsigned)off;
   off += (size_t)p.c_out * 256 * sizeof(float);
   sm.tab0 = base + (unsigned)off;
-  sm.wh_off = (unsigned)align16(kTabUrow + (size_t)4 * p.u_cap * sizeof(int2));
+  sm.wh_off = (unsigned)align16(kTabUrow + (size_t)8 * p.u_cap * sizeof(int2));
   sm.tab_stride = (unsigned)align16(sm.wh_off + (size_t)p.weight_floats * 2 * sizeof(float));
   off += 2 * (size_t)sm.tab_stride;
   sm.uw = base + (unsigned)off;
-  off += (size_t)4 * p.u_cap * 2 * sizeof(float4);
+  off += (size_t)8 * p.u_cap * sizeof(float4);
   sm.ucount = base + (unsigned)off;
-  off += 16;
+  off += 32;
   sm.bar = base + (unsigned)off;
   off += 16;
   sm.mid = base + (unsigned)off;
@@ -252,8 +344,8 @@ __host__ __device__ inline size_t smem_layout(const LaunchParams& p, unsigned ba
 struct PassGeom {
   int bx, nc;          // first geometric-output column and column count
   int clo, ncols;      // first source column staged, columns staged
-  int wbytes, pitch_s, nwords, common;
-  bool edge_x;
+  int wbytes, pitch_s, npairs, common;
+  bool edge_x, shifted;
   const uint8_t* g0;   // source byte of (first staged row, first staged column)
 };
 
@@ -271,15 +363,19 @@ __device__ __forceinline__ PassGeom pass_geom(const DevSample& s, const Axis& ax
   g.ncols = chi - g.clo + 1;
   g.wbytes = g.ncols * C;
   g.g0 = s.src + ((size_t)(s.pre_y + rlo) * s.src_w + (s.pre_x + g.clo)) * C;
-  g.common = (int)(reinterpret_cast<uintptr_t>(g.g0) & 3);
+  // rows whose pitch is a multiple of 8 all start at the same offset within an
+  // 8-byte unit, so a thread reads its two words with one aligned load; other
+  // sources take the funnel-shift path from 4-byte units
+  g.shifted = (((unsigned)s.src_w * C) & 7u) != 0;
+  g.common = (int)(reinterpret_cast<uintptr_t>(g.g0) & (g.shifted ? 3 : 7));
   g.pitch_s = (g.wbytes + 15 + 15 + 4 + 15) & ~15;
-  g.nwords = (g.common + g.wbytes + 3) >> 2;
+  g.npairs = (g.common + g.wbytes + 7) >> 3;
   return g;
 }
 
 // Issue the bulk copies of a pass (threads < rows) and build its tables
-// (threads 0..nc-1 the horizontal taps, the others the staged-row addresses of
-// the vertical union).
+// (the last kTileW threads the horizontal taps, all the staged-row addresses
+// of the vertical unions).
 template <int C>
 __device__ __forceinline__ void start_pass(
     const DevSample& s, const LaunchParams& p, const Smem& sm, unsigned tab, const PassGeom& g,
@@ -323,15 +419,16 @@ __device__ __forceinline__ void start_pass(
       }
     }
   }
-  const int ngroups = (nr + 3) >> 2;
-  for (int i = tid; i < ngroups * p.u_cap; i += kThreads) {
-    const int rg = i / p.u_cap;
-    const int e = i - rg * p.u_cap;
-    if (e < sp<int>(sm.ucount)[rg]) {
+  const int nrp = (nr + 1) >> 1;
+  for (int i = tid; i < nrp * p.u_cap; i += kThreads) {
+    const int rp = i / p.u_cap;
+    const int e = i - rp * p.u_cap;
+    if (e < sp<int>(sm.ucount)[rp]) {
       int lo, hi;
-      axis_range(ay, by + rg * 4, lo, hi);
+      axis_range(ay, by + rp * 2, lo, hi);
       const int sr = min(clampi(lo + e, 0, s.pre_h - 1) - rlo, rows - 1);
       const int phase = (int)((reinterpret_cast<uintptr_t>(g.g0) + (size_t)sr * src_pitch) & 15);
+      // aligned sources: boff is a multiple of 8 and the shift is unused
       const int boff = sr * g.pitch_s + phase - g.common;
       sp<int2>(tab + kTabUrow)[i] = make_int2((int)(sm.srct + (unsigned)(boff & ~3)), (boff & 3) * 8);
     }
@@ -368,19 +465,20 @@ __device__ void resize_rows(
   }
   first_use = false;
 
-  // ---- vertical union weights of every group of four output rows ---------------
-  for (int i = tid; i < ngroups * p.u_cap; i += kThreads) {
-    const int rg = i / p.u_cap;
-    const int e = i - rg * p.u_cap;
-    const int o0 = by + rg * 4;
-    const int on = min(4, nr - rg * 4);
-    int lo[4], hi[4];
+  // ---- vertical union weights of every pair of output rows ------------------------
+  const int nrp = (nr + 1) >> 1;
+  for (int i = tid; i < nrp * p.u_cap; i += kThreads) {
+    const int rp = i / p.u_cap;
+    const int e = i - rp * p.u_cap;
+    const int o0 = by + rp * 2;
+    const int on = min(2, nr - rp * 2);
+    int lo[2], hi[2];
 #pragma unroll
-    for (int r = 0; r < 4; r++) {
+    for (int r = 0; r < 2; r++) {
       axis_range(ay, o0 + (r < on ? r : on - 1), lo[r], hi[r]);
     }
     const int ufirst = lo[0];
-    const int ulast = hi[3];   // rows past the group's end repeat its last row
+    const int ulast = hi[1];   // a missing second row repeats the first
     const int u = ufirst + e;
     if (e == 0) {
       int cnt = ulast - ufirst + 1;
@@ -388,12 +486,12 @@ __device__ void resize_rows(
         cnt = p.u_cap;
         atomicOr(p.status, 8);
       }
-      sp<int>(sm.ucount)[rg] = cnt;
+      sp<int>(sm.ucount)[rp] = cnt;
     }
     if (u <= ulast) {
-      float w4[4];
+      float w2[2];
 #pragma unroll
-      for (int r = 0; r < 4; r++) {
+      for (int r = 0; r < 2; r++) {
         float w = 0.0f;
         if (r < on && u >= lo[r] && u <= hi[r]) {
           if (ay.identity) {
@@ -407,16 +505,15 @@ __device__ void resize_rows(
             w = __fdiv_rn(axis_tent(ay, c, u), sum);
           }
         }
-        w4[r] = w;
+        w2[r] = w;
       }
-      sp<float4>(sm.uw)[2 * i] = make_float4(w4[0], w4[0], w4[1], w4[1]);
-      sp<float4>(sm.uw)[2 * i + 1] = make_float4(w4[2], w4[2], w4[3], w4[3]);
+      sp<float4>(sm.uw)[i] = make_float4(w2[0], w2[0], w2[1], w2[1]);
     }
   }
   __syncthreads();   // ucount is read by start_pass
 
   PassGeom cur = pass_geom<C>(s, ax, rlo, gx_lo, min(s.sub_w, gx_hi - gx_lo));
-  if (rows * cur.pitch_s > p.src_tile_bytes || 4 * C * cur.ncols > p.mid_float4s) {
+  if (rows * cur.pitch_s > p.src_tile_bytes || ngroups * C * plane_slots<C>(cur.ncols) > p.mid_float4s) {
     if (tid == 0) {
       atomicOr(p.status, 2);
     }
@@ -440,101 +537,67 @@ __device__ void resize_rows(
     }
     parity ^= 1;
 
-    // ---- vertical filter: thread = (source word, group of four output rows) -----
+    // ---- vertical filter: thread = (eight byte columns, pair of output rows) --------
     {
-      // Rows start on a word boundary of the staging buffer whenever the source
-      // pitch is a multiple of four.
-      const bool shifted = (((unsigned)s.src_w * C) & 3u) != 0;
       const unsigned urow_base = tab + kTabUrow;
       const unsigned uw_base = sm.uw;
-      const int nw = cur.nwords;
-      // Two ways to deal the (row group, source word) pairs out.  Blocked: a
-      // half of the CTA per group, 128 words per round - every warp works on
-      // one group, so its table loads are broadcasts and the store offsets are
-      // shared by the groups.  Flat: one sequence over all pairs, which keeps
-      // the warps full when the word count is far from a multiple of 128.
-      const int blocked_slots = ((nw + 127) >> 7) * 128 * ((ngroups + 1) >> 1) * 2;
-      if (4 * nw * ngroups >= 3 * blocked_slots) {
-        for (int g = tid & 127; g < nw; g += 128) {
-          int off0, off1, off2, off3;
-          {
-            const int jb = 4 * g - cur.common;
-            int j = jb;
-            off0 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
-            j = jb + 1;
-            off1 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
-            j = jb + 2;
-            off2 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
-            j = jb + 3;
-            off3 = (j >= 0 && j < cur.wbytes) ? (j % C) * cur.ncols + j / C : -1;
-          }
-          for (int rg = tid >> 7; rg < ngroups; rg += kThreads >> 7) {
-            const int cnt = sp<int>(sm.ucount)[rg];
+      const int np = cur.npairs;
+      const int pslots = plane_slots<C>(cur.ncols);
+      const unsigned group_bytes = (unsigned)(C * pslots) * 16u;
+      // Two ways to deal the (row pair, column octet) items out.  Blocked: a
+      // quarter of the CTA per row pair, 64 octets per round - every warp works
+      // on one row pair, so its table loads are broadcasts and the store offsets
+      // serve every row pair.  Flat: one sequence over all items, which keeps
+      // the warps full when the octet count is far from a multiple of 64.
+      const int blocked_slots = ((np + 63) >> 6) * 64 * ((nrp + 3) >> 2) * 4;
+      if (4 * np * nrp >= 3 * blocked_slots) {
+        for (int g = tid & 63; g < np; g += 64) {
+          const int j0 = 8 * g - cur.common;
+          unsigned b0[C];
+          int low[C];
+          octet_offsets<C>(j0, pslots, b0, low);
+          for (int rp = tid >> 6; rp < nrp; rp += kThreads >> 6) {
+            const int cnt = sp<int>(sm.ucount)[rp];
             f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (shifted) {
-              vertical_taps<true>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
+            if (cur.shifted) {
+              vertical_taps<true>(urow_base + rp * p.u_cap * 8, uw_base + rp * p.u_cap * 16, 8u * g, cnt, acc);
             } else {
-              vertical_taps<false>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
+              vertical_taps<false>(urow_base + rp * p.u_cap * 8, uw_base + rp * p.u_cap * 16, 8u * g, cnt, acc);
             }
-            float a00, a01, a02, a03, a10, a11, a12, a13, a20, a21, a22, a23, a30, a31, a32, a33;
-            unpack2(acc[0], a00, a01);
-            unpack2(acc[1], a02, a03);
-            unpack2(acc[2], a10, a11);
-            unpack2(acc[3], a12, a13);
-            unpack2(acc[4], a20, a21);
-            unpack2(acc[5], a22, a23);
-            unpack2(acc[6], a30, a31);
-            unpack2(acc[7], a32, a33);
-            // planar store: column (px, ch) of group rg -> mid[(rg * C + ch) * ncols + px]
-            float4* plane = sp<float4>(sm.mid) + rg * C * cur.ncols;
-            if (off0 >= 0) plane[off0] = make_float4(a00, a10, a20, a30);
-            if (off1 >= 0) plane[off1] = make_float4(a01, a11, a21, a31);
-            if (off2 >= 0) plane[off2] = make_float4(a02, a12, a22, a32);
-            if (off3 >= 0) plane[off3] = make_float4(a03, a13, a23, a33);
+            // the pair's rows are one half of a float4 of its group of four rows
+            const unsigned pb = sm.mid + (unsigned)(rp >> 1) * group_bytes + (unsigned)(rp & 1) * 8u;
+            unsigned b[C];
+#pragma unroll
+            for (int m = 0; m < C; m++) {
+              b[m] = pb + b0[m];
+            }
+            store_octet<C>(b, low, acc);
           }
         }
       } else {
-        for (int i = tid; i < nw * ngroups; i += kThreads) {
-          const int rg = (i >= nw ? 1 : 0) + (i >= 2 * nw ? 1 : 0) + (i >= 3 * nw ? 1 : 0);
-          const int g = i - rg * nw;
-          const int cnt = sp<int>(sm.ucount)[rg];
+        const float inv_np = 1.0f / (float)np;
+        for (int i = tid; i < np * nrp; i += kThreads) {
+          int rp = (int)((float)i * inv_np);
+          rp -= (rp * np > i) ? 1 : 0;
+          rp += ((rp + 1) * np <= i) ? 1 : 0;
+          const int g = i - rp * np;
+          const int cnt = sp<int>(sm.ucount)[rp];
           f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          if (shifted) {
-            vertical_taps<true>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
+          if (cur.shifted) {
+            vertical_taps<true>(urow_base + rp * p.u_cap * 8, uw_base + rp * p.u_cap * 16, 8u * g, cnt, acc);
           } else {
-            vertical_taps<false>(urow_base + rg * p.u_cap * 8, uw_base + rg * p.u_cap * 32, 4u * g, cnt, acc);
+            vertical_taps<false>(urow_base + rp * p.u_cap * 8, uw_base + rp * p.u_cap * 16, 8u * g, cnt, acc);
           }
-          // planar store: byte column j = (px, ch) of group rg -> mid[(rg * C + ch) * ncols + px];
-          // quotient and remainder by C advance with j
-          float4* plane = sp<float4>(sm.mid) + rg * C * cur.ncols;
-          const int j0 = 4 * g - cur.common;
-          int q = (j0 + 4 * C) / C - 4;
-          int r = (j0 + 4 * C) - (q + 4) * C;
-  #pragma unroll
-          for (int k = 0; k < 2; k++) {
-            float lo0, hi0, lo1, hi1, lo2, hi2, lo3, hi3;
-            unpack2(acc[0 + k], lo0, hi0);
-            unpack2(acc[2 + k], lo1, hi1);
-            unpack2(acc[4 + k], lo2, hi2);
-            unpack2(acc[6 + k], lo3, hi3);
-            const int j = j0 + 2 * k;
-            if (j >= 0 && j < cur.wbytes) {
-              plane[r * cur.ncols + q] = make_float4(lo0, lo1, lo2, lo3);
-            }
-            r++;
-            if (r == C) {
-              r = 0;
-              q++;
-            }
-            if (j + 1 >= 0 && j + 1 < cur.wbytes) {
-              plane[r * cur.ncols + q] = make_float4(hi0, hi1, hi2, hi3);
-            }
-            r++;
-            if (r == C) {
-              r = 0;
-              q++;
-            }
+          const int j0 = 8 * g - cur.common;
+          unsigned b[C];
+          int low[C];
+          octet_offsets<C>(j0, pslots, b, low);
+          const unsigned pb = sm.mid + (unsigned)(rp >> 1) * group_bytes + (unsigned)(rp & 1) * 8u;
+#pragma unroll
+          for (int m = 0; m < C; m++) {
+            b[m] += pb;
           }
+          store_octet<C>(b, low, acc);
         }
       }
     }
@@ -546,7 +609,7 @@ __device__ void resize_rows(
     PassGeom nxt = cur;
     if (more) {
       nxt = pass_geom<C>(s, ax, rlo, next_bx, min(s.sub_w, gx_hi - next_bx));
-      if (rows * nxt.pitch_s > p.src_tile_bytes || 4 * C * nxt.ncols > p.mid_float4s) {
+      if (rows * nxt.pitch_s > p.src_tile_bytes || ngroups * C * plane_slots<C>(nxt.ncols) > p.mid_float4s) {
         if (tid == 0) {
           atomicOr(p.status, 2);
         }
@@ -558,7 +621,7 @@ __device__ void resize_rows(
 
     // ---- horizontal filter: thread = (output column, group of four rows), all channels ----
     {
-      const unsigned plane = (unsigned)cur.ncols * 16u;
+      const unsigned plane = (unsigned)plane_slots<C>(cur.ncols) * 16u;
       for (int item = tid; item < ngroups * cur.nc; item += kThreads) {
         int rg, x;
         if (cur.nc == kTileW) {
@@ -579,32 +642,35 @@ __device__ void resize_rows(
           acc[c][0] = 0;
           acc[c][1] = 0;
         }
-        if (!cur.edge_x) {
-          unsigned cp[C];
+        unsigned cb[C];   // the group's plane of every channel
 #pragma unroll
-          for (int c = 0; c < C; c++) {
-            cp[c] = col_a + (unsigned)(f - cur.clo) * 16u + (unsigned)c * plane;
-          }
+        for (int c = 0; c < C; c++) {
+          cb[c] = col_a + (unsigned)c * plane;
+        }
+        if (!cur.edge_x) {
+          int col = PlanePad<C>::value + f - cur.clo;
           while (wq != wq_end) {
             const f32x2 wk = lds_u64<0>(wq);
+            const unsigned off = (unsigned)skew(col) * 16u;
 #pragma unroll
             for (int c = 0; c < C; c++) {
               f32x2 v01, v23;
-              lds_v2u64<0>(cp[c], v01, v23);
+              lds_v2u64<0>(cb[c] + off, v01, v23);
               ffma2(acc[c][0], v01, wk);
               ffma2(acc[c][1], v23, wk);
-              cp[c] += 16;
             }
+            col++;
             wq += 8;
           }
         } else {
           for (int k = 0; wq != wq_end; k++) {
             const f32x2 wk = lds_u64<0>(wq);
-            const unsigned ca = col_a + (unsigned)(clampi(f + k, 0, s.pre_w - 1) - cur.clo) * 16u;
+            const unsigned off =
+                (unsigned)skew(PlanePad<C>::value + clampi(f + k, 0, s.pre_w - 1) - cur.clo) * 16u;
 #pragma unroll
             for (int c = 0; c < C; c++) {
               f32x2 v01, v23;
-              lds_v2u64<0>(ca + (unsigned)c * plane, v01, v23);
+              lds_v2u64<0>(cb[c] + off, v01, v23);
               ffma2(acc[c][0], v01, wk);
               ffma2(acc[c][1], v23, wk);
             }

@@ -122,11 +122,11 @@ extern "C" int mlxd_fused_batch_noalloc(
   PassNeed need = PassNeed{0, 0, 0, 0, 0};
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)batch->slot_h * batch->slot_w * p.c_out * esize;
+  rc = plan_into(samples, n, batch, table, need);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
   for (int i = 0; i < n; i++) {
-    rc = plan_one_sample(samples[i], i, batch, table[i], need);
-    if (rc != MLXD_OK) {
-      return rc;
-    }
     table[i].dst = static_cast<uint8_t*>(batch->dst) + slot_bytes * i;
   }
   p.src_tile_bytes = need.src_bytes;
