@@ -236,3 +236,40 @@ def test_errors(pkg, ctx):
     ctx.wait(0)
     s = ctx.stats()
     assert s["kernel_launches"] > 0 and s["h2d_bytes"] > 0
+
+
+# ---------------------------------------------------------------- float32 kernel, resize corner cases
+FAST_RESIZE_CASES = [
+    # (source H, W), channels, ops: pitches that are / are not multiples of 8 bytes, up- and down-scaling,
+    # ratios that force smaller passes, windows at odd offsets, mirrored outputs, tiny images
+    ((96, 128), 3, [("image_resize", dict(key="image", w=61, h=47))]),
+    ((96, 128), 1, [("image_resize", dict(key="image", w=61, h=47))]),
+    ((96, 128), 4, [("image_resize", dict(key="image", w=61, h=47))]),
+    ((97, 131), 3, [("image_resize", dict(key="image", w=200, h=150))]),
+    ((97, 131), 1, [("image_resize", dict(key="image", w=33, h=29)), ("image_random_h_flip", dict(key="image", prob=1.0))]),
+    ((97, 131), 4, [("image_resize", dict(key="image", w=131, h=40))]),
+    ((513, 777), 3, [("image_center_crop", dict(key="image", w=701, h=451)),
+                     ("image_resize", dict(key="image", w=90, h=70)),
+                     ("image_center_crop", dict(key="image", w=77, h=63))]),
+    ((700, 1100), 3, [("image_resize", dict(key="image", w=37, h=25))]),
+    ((600, 40), 3, [("image_resize", dict(key="image", w=40, h=19))]),
+    ((5, 3), 3, [("image_resize", dict(key="image", w=67, h=130))]),
+    ((1, 1), 4, [("image_resize", dict(key="image", w=17, h=3))]),
+    ((240, 320), 3, [("image_resize_smallest_side", dict(key="image", size=96)),
+                     ("image_random_h_flip", dict(key="image", prob=1.0)),
+                     ("image_center_crop", dict(key="image", w=80, h=80))]),
+]
+
+
+@pytest.mark.parametrize("case", range(len(FAST_RESIZE_CASES)))
+@pytest.mark.parametrize("cast", [(), "norm"])
+def test_float32_resize_cases(pkg, ctx, oracle, case, cast):
+    (h, w), c, ops = FAST_RESIZE_CASES[case]
+    rng = np.random.default_rng(100 + case)
+    # three samples per batch, the later ones one row / column smaller: ragged slots and padding
+    samples = [{"image": rng.integers(0, 256, (max(1, h - i), max(1, w - 2 * i), c), dtype=np.uint8)} for i in range(3)]
+    if cast == "norm":
+        cast = ([0.485, 0.456, 0.406, 0.5][:c], [0.229, 0.224, 0.225, 0.25][:c])
+    want = _oracle_batches(oracle, samples, ops, 3, cast, 5.0)
+    got = _fused_batches(pkg, ctx, oracle, samples, ops, 3, cast, 5.0)
+    _compare(got, want, True, cast)
