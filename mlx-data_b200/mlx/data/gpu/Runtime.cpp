@@ -61,6 +61,16 @@ LazyImage::LazyImage(const std::shared_ptr<const Array>& src) : src_(src) {
   post_ = Window{0, 0, pre_.w, pre_.h, false};
 }
 
+LazyImage LazyImage::with_source(const std::shared_ptr<const Array>& src) const {
+  if (src->ndim() != 3 || src->shape(0) != src_->shape(0) || src->shape(1) != src_->shape(1) ||
+      src->shape(2) != src_->shape(2)) {
+    throw std::runtime_error("LazyImage: a program moves only to a source of the same shape");
+  }
+  LazyImage out(*this);
+  out.src_ = src;
+  return out;
+}
+
 int64_t LazyImage::width() const {
   return post_.w;
 }

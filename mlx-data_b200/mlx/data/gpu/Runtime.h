@@ -49,6 +49,8 @@ class LazyImage {
   // True while no op has been folded in: the result is the source itself.
   bool untouched() const { return untouched_; }
   const std::shared_ptr<const Array>& source() const { return src_; }
+  // The same program on another source of the same shape (the frames of a clip).
+  LazyImage with_source(const std::shared_ptr<const Array>& src) const;
 
   void crop(int64_t x, int64_t y, int64_t w, int64_t h);
   void hflip();

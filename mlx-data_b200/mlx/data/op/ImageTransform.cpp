@@ -27,7 +27,7 @@ Sample ImageTransformOp::apply(const Sample& sample) const {
   auto src = sample::check_key(sample, ikey_, ArrayType::Any);
   Sample res = sample;
   if (src->ndim() == 4) {
-    res[output_key()] = apply_video(src);
+    res[output_key()] = apply_clip(src, &sample);
     return res;
   }
   gpu::LazyImage lazy(src);
@@ -57,9 +57,51 @@ std::shared_ptr<Array> ImageTransformOp::apply_image(const std::shared_ptr<const
   return lazy.materialise();
 }
 
-std::shared_ptr<Array> ImageTransformOp::apply_video(const std::shared_ptr<const Array>&) const {
-  throw std::runtime_error(
-      "ImageTransformOp: 4 dimension (video) arrays are not handled by the GPU image path");
+std::shared_ptr<Array> ImageTransformOp::apply_video(const std::shared_ptr<const Array>& video) const {
+  return apply_clip(video, nullptr);
+}
+
+std::shared_ptr<Array> ImageTransformOp::apply_clip(
+    const std::shared_ptr<const Array>& video, const Sample* sample) const {
+  // the checks of core::video::verify_video
+  if (video->ndim() != 4) {
+    throw std::runtime_error("verifyVideo: video must be 4 dimension Array (FHWC)");
+  }
+  const int64_t frames = video->shape(0);
+  const int64_t h = video->shape(1);
+  const int64_t w = video->shape(2);
+  const int64_t c = video->shape(3);
+  if (c == 0 || c > 4) {
+    throw std::runtime_error("verifyVideo: channels must be 0 <= c <= 4");
+  }
+  if (video->type() != ArrayType::UInt8) {
+    throw std::runtime_error("ImageTransformOp: clips must be uint8");
+  }
+  if (frames == 0) {
+    throw std::runtime_error("ImageTransformOp: clip without frames");
+  }
+  const size_t frame_bytes = static_cast<size_t>(h) * w * c;
+  auto frame = [&](int64_t f) {
+    // a view of frame f that keeps the clip's storage alive
+    std::shared_ptr<void> at(video->storage(), static_cast<uint8_t*>(video->data()) + f * frame_bytes);
+    return std::make_shared<const Array>(ArrayType::UInt8, std::vector<int64_t>{h, w, c}, at, video->device());
+  };
+  gpu::LazyImage first(frame(0));
+  const bool ok = sample ? fold_in(first, *sample) : fold(first);
+  if (!ok) {
+    throw std::runtime_error("ImageTransformOp: internal error: op does not fold into an empty program");
+  }
+  if (first.untouched()) {
+    return std::make_shared<Array>(video);
+  }
+  std::vector<gpu::LazyImage> all;
+  all.reserve(frames);
+  all.push_back(first);
+  for (int64_t f = 1; f < frames; f++) {
+    all.push_back(first.with_source(frame(f)));
+  }
+  // every frame has the same result size: the "batch" is the clip, nothing is padded
+  return gpu::Runtime::get().batch(all, 0.0, nullptr);
 }
 
 // ------------------------------------------------------------ resize

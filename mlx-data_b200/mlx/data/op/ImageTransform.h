@@ -35,6 +35,13 @@ class ImageTransformOp : public KeyTransformOp {
     return fold(image);
   }
   virtual bool reads_sample() const { return false; }
+
+ private:
+  // A clip [F, H, W, C]: the op is recorded once, on the first frame - so random
+  // parameters are drawn once per clip, as the per-op video variants of
+  // mlx-data do (mlx/data/op/ImageTransform.cpp:33-70, 160-182, 293-357) - and
+  // every frame runs that program in one launch.
+  std::shared_ptr<Array> apply_clip(const std::shared_ptr<const Array>& video, const Sample* sample) const;
 };
 
 class ImageResizeSmallestSide : public ImageTransformOp {

@@ -134,3 +134,36 @@ def test_error_behaviour_matches(pkg):
         pkg.buffer_from_vector([{"image": np.zeros((4, 4, 3), np.float32)}]).image_resize("image", 2, 2)[0]
     with pytest.raises(IndexError):
         b[3]
+
+
+CLIP_CHAINS = {
+    "resize_crop_flip": [("image_resize_smallest_side", dict(key="image", size=48)),
+                         ("image_random_crop", dict(key="image", w=40, h=36)),
+                         ("image_random_h_flip", dict(key="image", prob=0.5))],
+    "area_crop_resize": [("image_random_area_crop", dict(key="image", area_range=(0.3, 1.0),
+                                                          aspect_ratio_range=(0.75, 4 / 3))),
+                         ("image_resize", dict(key="image", w=32, h=24))],
+    "rotate_gray": [("image_rotate", dict(key="image", angle=20.0, crop=True)),
+                    ("image_channel_reduction", dict(key="image", preset="default"))],
+    "center_crop_only": [("image_center_crop", dict(key="image", w=30, h=20))],
+}
+
+
+@pytest.mark.parametrize("name", sorted(CLIP_CHAINS))
+def test_clips_through_stream_api(pkg, name):
+    """4-D [F, H, W, C] entries: every frame gets the op, random parameters are
+    drawn once per clip (mlx/data/op/ImageTransform.cpp:33-70, 160-182, 293-357)."""
+    if refpipe.reference_module() is None:
+        pytest.skip("needs the reference compiled under oracle/_ref")
+    ops = CLIP_CHAINS[name]
+    rng = np.random.default_rng(77)
+    samples = []
+    for i in range(6):
+        f, h, w = int(rng.integers(2, 6)), int(rng.integers(50, 90)), int(rng.integers(50, 90))
+        samples.append({"image": rng.integers(0, 256, (f, h, w, 3), dtype=np.uint8), "label": np.int64(i)})
+    keys = {"image": ()}
+    want = refpipe.run_reference(samples, ops, 2, {"image": 9.0}, keys, seed=5)
+    pkg.core.set_state(5)
+    got = [dict(b) for b in refpipe.build(pkg, samples, ops, 2, {"image": 9.0}, keys, native_cast=True, product=True)]
+    has_resize = any(n.startswith("image_resize") for n, _ in ops)
+    _check(got, want, has_resize, 1.0 / 255)
