@@ -356,7 +356,7 @@ def main():
             a = dx.core.pinned_empty([h, w, 3], "uint8")
             a[...] = rng.integers(0, 256, (h, w, 3), dtype=np.uint8)
             host_pool.append(a)
-        lanes = 4
+        lanes = int(os.environ.get("MLXD_BENCH_LANES", "4"))
         # Warm-up on a pipeline of its own, fully consumed.  Page-locked batch
         # buffers are expensive to allocate (about half a second per GB) and are
         # recycled afterwards; 2 * lanes + 2 batches bring the pool to the number

@@ -165,16 +165,24 @@ void* mlxd_pinned_alloc(size_t bytes) {
   if (bytes == 0) {
     bytes = 1;
   }
-  cudaError_t e = cudaHostAlloc(&p, bytes, cudaHostAllocPortable);
+  cudaError_t e = cudaHostAlloc(&p, bytes, cudaHostAllocPortable | cudaHostAllocMapped);
   if (e != cudaSuccess) {
     fail_cuda(e, "cudaHostAlloc");
     return nullptr;
+  }
+  // Remember the block: sources inside it can be read by the gather kernel.
+  void* dp = nullptr;
+  if (cudaHostGetDevicePointer(&dp, p, 0) == cudaSuccess && dp != nullptr) {
+    mlxd::pinned_registry_add(p, bytes, dp);
+  } else {
+    cudaGetLastError();
   }
   return p;
 }
 
 void mlxd_pinned_free(void* p) {
   if (p) {
+    mlxd::pinned_registry_remove(p);
     cudaFreeHost(p);
   }
 }

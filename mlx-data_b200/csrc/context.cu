@@ -1,6 +1,8 @@
 // Context, lanes, descriptor planning and the enqueue path of the C ABI.
 #include "context.h"
 
+#include <map>
+
 #include <chrono>
 #include <cmath>
 #include <cstdlib>
@@ -33,6 +35,40 @@ int fail_cuda(cudaError_t e, const char* what) {
 
 bool LutKey::operator<(const LutKey& o) const {
   return std::memcmp(this, &o, sizeof(LutKey)) < 0;
+}
+
+namespace {
+struct PinnedBlock {
+  size_t bytes;
+  intptr_t device_delta;   // device-side address minus host address
+};
+std::mutex g_pinned_mu;
+std::map<uintptr_t, PinnedBlock> g_pinned;
+}  // namespace
+
+void pinned_registry_add(void* host, size_t bytes, void* device_side) {
+  std::lock_guard<std::mutex> g(g_pinned_mu);
+  g_pinned[reinterpret_cast<uintptr_t>(host)] =
+      PinnedBlock{bytes, static_cast<intptr_t>(reinterpret_cast<uintptr_t>(device_side) - reinterpret_cast<uintptr_t>(host))};
+}
+
+void pinned_registry_remove(void* host) {
+  std::lock_guard<std::mutex> g(g_pinned_mu);
+  g_pinned.erase(reinterpret_cast<uintptr_t>(host));
+}
+
+const uint8_t* pinned_registry_lookup(const void* host) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(host);
+  std::lock_guard<std::mutex> g(g_pinned_mu);
+  auto it = g_pinned.upper_bound(a);
+  if (it == g_pinned.begin()) {
+    return nullptr;
+  }
+  --it;
+  if (a >= it->first + it->second.bytes) {
+    return nullptr;
+  }
+  return reinterpret_cast<const uint8_t*>(a + it->second.device_delta);
 }
 
 int arena_reserve(mlxd_ctx* ctx, Arena& a, size_t bytes, bool pinned, cudaStream_t stream_to_drain) {
@@ -411,11 +447,14 @@ int enqueue_on_lane(
   // The pinned descriptor table of this slot may still be in flight.
   MLXD_CUDA(cudaEventSynchronize(lane.desc_copied[slot]));
   harvest_timing(ctx, lane, slot, true);
-  rc = arena_reserve(ctx, lane.h_desc[slot], sizeof(DevSample) * n, true, lane.stream);
+  // descriptors, then (for host sources) the table of the gather kernel
+  const size_t desc_bytes = (sizeof(DevSample) * n + 255) & ~(size_t)255;
+  const size_t block_bytes = desc_bytes + sizeof(GatherPiece) * n;
+  rc = arena_reserve(ctx, lane.h_desc[slot], block_bytes, true, lane.stream);
   if (rc != MLXD_OK) {
     return rc;
   }
-  rc = arena_reserve(ctx, lane.d_desc[slot], sizeof(DevSample) * n, false, lane.stream);
+  rc = arena_reserve(ctx, lane.d_desc[slot], block_bytes, false, lane.stream);
   if (rc != MLXD_OK) {
     return rc;
   }
@@ -435,6 +474,24 @@ int enqueue_on_lane(
   }
   ctx->algo_src += algo_src;
   ctx->algo_dst += out_bytes;
+  // Page-locked sources that the GPU can address are packed by a kernel that
+  // reads exactly the needed rectangles (gather.cu); anything else goes
+  // through the copy engines.  MLXD_HOST_GATHER=0 turns the kernel path off.
+  bool gather = false;
+  std::vector<const uint8_t*> src_dev;
+  if (host_src) {
+    static const bool gather_enabled = [] {
+      const char* v = std::getenv("MLXD_HOST_GATHER");
+      return !(v && *v == '0');
+    }();
+    gather = gather_enabled;
+    src_dev.resize(n);
+    // sources in blocks from mlxd_pinned_alloc: a table look-up, no driver call
+    for (int i = 0; i < n && gather; i++) {
+      src_dev[i] = pinned_registry_lookup(samples[i].src);
+      gather = src_dev[i] != nullptr;
+    }
+  }
   if (host_src) {
     pieces.resize(n);
     for (int i = 0; i < n; i++) {
@@ -447,7 +504,7 @@ int enqueue_on_lane(
         const char* v = std::getenv("MLXD_TRIM_PERCENT");
         return v && *v ? std::atoi(v) : 60;
       }();
-      if ((int64_t)(dev[i].src_w - (c1 - c0)) * 100 < (int64_t)trim_percent * dev[i].src_w) {
+      if (!gather && (int64_t)(dev[i].src_w - (c1 - c0)) * 100 < (int64_t)trim_percent * dev[i].src_w) {
         c0 = 0;
         c1 = dev[i].src_w;
       }
@@ -486,10 +543,35 @@ int enqueue_on_lane(
   }
 
   std::memcpy(lane.h_desc[slot].ptr, dev.data(), sizeof(DevSample) * n);
-  MLXD_CUDA(cudaMemcpyAsync(
-      lane.d_desc[slot].ptr, lane.h_desc[slot].ptr, sizeof(DevSample) * n, cudaMemcpyHostToDevice, lane.stream));
+  size_t upload = sizeof(DevSample) * n;
+  uint32_t gather_rows = 0;
+  if (gather) {
+    GatherPiece* gp = reinterpret_cast<GatherPiece*>(static_cast<uint8_t*>(lane.h_desc[slot].ptr) + desc_bytes);
+    for (int i = 0; i < n; i++) {
+      gp[i].src = src_dev[i] + (pieces[i].from - samples[i].src);
+      gp[i].dst = static_cast<uint8_t*>(lane.d_src.ptr) + pieces[i].offset;
+      gp[i].src_pitch = pieces[i].from_pitch;
+      gp[i].rows = (uint32_t)pieces[i].rows;
+      gp[i].row_bytes = (uint32_t)pieces[i].row_bytes;
+      gp[i].first_row = gather_rows;
+      gp[i].pad_ = 0;
+      gather_rows += (uint32_t)pieces[i].rows;
+    }
+    upload = block_bytes;
+  }
+  MLXD_CUDA(cudaMemcpyAsync(lane.d_desc[slot].ptr, lane.h_desc[slot].ptr, upload, cudaMemcpyHostToDevice, lane.stream));
   MLXD_CUDA(cudaEventRecord(lane.desc_copied[slot], lane.stream));
-  if (host_src) {
+  if (gather) {
+    const GatherPiece* gd =
+        reinterpret_cast<const GatherPiece*>(static_cast<const uint8_t*>(lane.d_desc[slot].ptr) + desc_bytes);
+    MLXD_CUDA(launch_gather_rows(gd, n, gather_rows, lane.stream));
+    ctx->launches += 1;
+    uint64_t moved = 0;
+    for (int i = 0; i < n; i++) {
+      moved += (uint64_t)pieces[i].row_bytes * pieces[i].rows;
+    }
+    ctx->h2d += moved;
+  } else if (host_src) {
     for (int i = 0; i < n; i++) {
       uint8_t* to = static_cast<uint8_t*>(lane.d_src.ptr) + pieces[i].offset;
       if (pieces[i].row_bytes == pieces[i].from_pitch) {

@@ -84,6 +84,26 @@ int plan_samples(
     std::vector<DevSample>& out, PassNeed& need);
 
 // One sample of plan_samples; `need` accumulates the shared-memory bounds.
+// One rectangle of a host source that gather.cu packs into device memory:
+// `rows` rows of `row_bytes` bytes, `src_pitch` apart at the source (a pointer
+// the GPU can dereference), tightly packed at `dst`.  `first_row` is the number
+// of rows of all earlier pieces of the launch.
+struct GatherPiece {
+  const uint8_t* src;
+  uint8_t* dst;
+  uint64_t src_pitch;
+  uint32_t rows, row_bytes;
+  uint32_t first_row, pad_;
+};
+// Blocks handed out by mlxd_pinned_alloc, with the address the GPU uses for
+// them.  pinned_registry_lookup returns the device-side pointer for a host
+// pointer inside a registered block, nullptr otherwise.
+void pinned_registry_add(void* host, size_t bytes, void* device_side);
+void pinned_registry_remove(void* host);
+const uint8_t* pinned_registry_lookup(const void* host);
+
+cudaError_t launch_gather_rows(const GatherPiece* table_dev, int n, uint32_t total_rows, cudaStream_t stream);
+
 int plan_one_sample(
     const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, DevSample& out, PassNeed& need, long long pass_budget);
 // plan_samples into caller-owned storage of n entries.

@@ -167,3 +167,31 @@ def test_clips_through_stream_api(pkg, name):
     got = [dict(b) for b in refpipe.build(pkg, samples, ops, 2, {"image": 9.0}, keys, native_cast=True, product=True)]
     has_resize = any(n.startswith("image_resize") for n, _ in ops)
     _check(got, want, has_resize, 1.0 / 255)
+
+
+def test_pinned_sources_are_gathered(pkg):
+    """Samples in page-locked memory are staged by the gather kernel: only the
+    rectangle each chain reads crosses the bus, and the batches do not change."""
+    rng = np.random.default_rng(31)
+    ops = [("image_center_crop", dict(key="image", w=61, h=45)),
+           ("image_resize", dict(key="image", w=40, h=52)),
+           ("image_random_h_flip", dict(key="image", prob=0.5))]
+    plain, pinned = [], []
+    for i in range(10):
+        h, w = int(rng.integers(70, 130)), int(rng.integers(90, 170))
+        img = rng.integers(0, 256, (h, w, 3), dtype=np.uint8)
+        plain.append({"image": img})
+        buf = pkg.core.pinned_empty([h, w, 3], "uint8")
+        np.asarray(buf)[...] = img
+        pinned.append({"image": buf})
+    keys = {"image": ()}
+    want = refpipe.run_reference(plain, ops, 4, {"image": 0.0}, keys, seed=9)
+    pkg.core.set_state(9)
+    s0 = pkg.core.stats()
+    got = [dict(b) for b in refpipe.build(pkg, pinned, ops, 4, {"image": 0.0}, keys, native_cast=True, product=True)]
+    s1 = pkg.core.stats()
+    _check(got, want, True, 1.0 / 255)
+    full = sum(s["image"].shape[0] * s["image"].shape[1] * 3 for s in plain)
+    moved = s1["h2d_bytes"] - s0["h2d_bytes"]
+    # a 61 x 45 window (plus filter margin) of images of at least 90 x 70 pixels
+    assert 0 < moved < 0.8 * full, (moved, full)
