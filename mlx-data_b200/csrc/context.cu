@@ -142,7 +142,7 @@ static int check_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc*
 static long long pass_bytes(const PassNeed& n) {
   return (long long)n.src_bytes + 16LL * n.mid_float4s + 16LL * n.weight_floats + 256LL * n.u_cap;
 }
-constexpr long long kPassBudgetBytes = 70 * 1024;
+constexpr long long kPassBudgetBytes = 69 * 1024;
 
 static int plan_resize(DevSample& s, int C, int i, PassNeed& need, long long pass_budget) {
   // First look for the largest pass within the three-CTA budget, not going

@@ -304,6 +304,7 @@ struct Smem {
   unsigned wh_off;
   unsigned uw;          // float4 [8][u_cap]  (w0,w0,w1,w1): weight of a union row in the two outputs of a row pair
   unsigned ucount;      // int [8]  rows in each row pair's union
+  unsigned ufirst;      // int [8]  first (unclamped) source row of each row pair's union
   unsigned bar;
   unsigned mid;         // float4 [4][C][plane_slots]
   unsigned srct;
@@ -330,6 +331,8 @@ __host__ __device__ inline size_t smem_layout(const LaunchParams& p, unsigned ba
   sm.uw = base + (unsigned)off;
   off += (size_t)8 * p.u_cap * sizeof(float4);
   sm.ucount = base + (unsigned)off;
+  off += 32;
+  sm.ufirst = base + (unsigned)off;
   off += 32;
   sm.bar = base + (unsigned)off;
   off += 16;
@@ -382,7 +385,7 @@ __device__ __forceinline__ PassGeom pass_geom(const DevSample& s, const Axis& ax
 template <int C>
 __device__ __forceinline__ void start_pass(
     const DevSample& s, const LaunchParams& p, const Smem& sm, unsigned tab, const PassGeom& g,
-    const Axis& ay, const Axis& ax, int by, int nr, int rlo, int rows) {
+    const Axis& ax, int nr, int rlo, int rows) {
   const int tid = threadIdx.x;
   const size_t src_pitch = (size_t)s.src_w * C;
   if (tid < rows) {
@@ -422,18 +425,19 @@ __device__ __forceinline__ void start_pass(
       }
     }
   }
+  // staged-row addresses: warp rp takes row pair rp (at most kTileH / 2 = 8 of them)
   const int nrp = (nr + 1) >> 1;
-  for (int i = tid; i < nrp * p.u_cap; i += kThreads) {
-    const int rp = i / p.u_cap;
-    const int e = i - rp * p.u_cap;
-    if (e < sp<int>(sm.ucount)[rp]) {
-      int lo, hi;
-      axis_range(ay, by + rp * 2, lo, hi);
-      const int sr = min(clampi(lo + e, 0, s.pre_h - 1) - rlo, rows - 1);
+  const int rp = tid >> 5;
+  if (rp < nrp) {
+    const int cnt = sp<int>(sm.ucount)[rp];
+    const int first = sp<int>(sm.ufirst)[rp];
+    for (int e = tid & 31; e < cnt; e += 32) {
+      const int sr = min(clampi(first + e, 0, s.pre_h - 1) - rlo, rows - 1);
       const int phase = (int)((reinterpret_cast<uintptr_t>(g.g0) + (size_t)sr * src_pitch) & 15);
       // aligned sources: boff is a multiple of 8 and the shift is unused
       const int boff = sr * g.pitch_s + phase - g.common;
-      sp<int2>(tab + kTabUrow)[i] = make_int2((int)(sm.srct + (unsigned)(boff & ~3)), (boff & 3) * 8);
+      sp<int2>(tab + kTabUrow)[rp * p.u_cap + e] =
+          make_int2((int)(sm.srct + (unsigned)(boff & ~3)), (boff & 3) * 8);
     }
   }
 }
@@ -490,6 +494,7 @@ __device__ void resize_rows(
         atomicOr(p.status, 8);
       }
       sp<int>(sm.ucount)[rp] = cnt;
+      sp<int>(sm.ufirst)[rp] = ufirst;
     }
     if (u <= ulast) {
       float w2[2];
@@ -522,7 +527,7 @@ __device__ void resize_rows(
     }
     return;
   }
-  start_pass<C>(s, p, sm, sm.tab0, cur, ay, ax, by, nr, rlo, rows);
+  start_pass<C>(s, p, sm, sm.tab0, cur, ax, nr, rlo, rows);
   __syncthreads();
   if (tid == 0) {
     mbar_arrive(sm.bar);
@@ -619,7 +624,7 @@ __device__ void resize_rows(
         return;
       }
       fence_async_smem();
-      start_pass<C>(s, p, sm, tab_next, nxt, ay, ax, by, nr, rlo, rows);
+      start_pass<C>(s, p, sm, tab_next, nxt, ax, nr, rlo, rows);
     }
 
     // ---- horizontal filter: thread = (output column, group of four rows), all channels ----
