@@ -25,6 +25,15 @@ class Buffer : public Dataset<Buffer, buffer::Buffer> {
   Buffer batch(
       const std::vector<int64_t>& batch_sizes, const std::unordered_map<std::string, double>& pad_values = {},
       const std::unordered_map<std::string, int>& batch_dims = {}) const;
+  // Batches of about the same padded element count (mlx/data/Buffer.h dynamic_batch).
+  Buffer dynamic_batch(
+      const std::string& key, int64_t min_data_size = -1, int64_t max_data_size = -1,
+      const std::unordered_map<std::string, double>& pad_values = {},
+      const std::unordered_map<std::string, int>& batch_dims = {}, bool drop_outliers = false) const;
+  Buffer dynamic_batch(
+      const Buffer& size_buffer, const std::string& key, int64_t min_data_size = -1, int64_t max_data_size = -1,
+      const std::unordered_map<std::string, double>& pad_values = {},
+      const std::unordered_map<std::string, int>& batch_dims = {}, bool drop_outliers = false) const;
   Stream ordered_prefetch(int prefetch_size, int num_thread) const;
   Buffer partition(int64_t num_partitions, int64_t partition) const;
   Buffer partition_if(bool cond, int64_t num_partitions, int64_t partition) const;

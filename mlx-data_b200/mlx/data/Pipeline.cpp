@@ -78,6 +78,22 @@ Buffer Buffer::batch(
   return Buffer(std::make_shared<buffer::Batch>(self_, batch_sizes, pad_values, batch_dims));
 }
 
+Buffer Buffer::dynamic_batch(
+    const std::string& key, int64_t min_data_size, int64_t max_data_size,
+    const std::unordered_map<std::string, double>& pad_values, const std::unordered_map<std::string, int>& batch_dims,
+    bool drop_outliers) const {
+  return Buffer(buffer::dynamic_batch(
+      self_, nullptr, key, min_data_size, max_data_size, pad_values, batch_dims, drop_outliers));
+}
+
+Buffer Buffer::dynamic_batch(
+    const Buffer& size_buffer, const std::string& key, int64_t min_data_size, int64_t max_data_size,
+    const std::unordered_map<std::string, double>& pad_values, const std::unordered_map<std::string, int>& batch_dims,
+    bool drop_outliers) const {
+  return Buffer(buffer::dynamic_batch(
+      self_, size_buffer.self_, key, min_data_size, max_data_size, pad_values, batch_dims, drop_outliers));
+}
+
 Stream Buffer::ordered_prefetch(int prefetch_size, int num_thread) const {
   return Stream(std::make_shared<stream::OrderedPrefetch>(self_, prefetch_size, num_thread));
 }

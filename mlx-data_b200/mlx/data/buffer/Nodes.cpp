@@ -189,6 +189,202 @@ int64_t Partition::size() const {
   return size_;
 }
 
+// ------------------------------------------------------------ Perm
+Perm::Perm(const std::shared_ptr<Buffer>& source, const std::vector<int64_t>& perm) : source_(source), perm_(perm) {
+  const int64_t n = source->size();
+  for (auto i : perm_) {
+    if (i < 0 || i >= n) {
+      throw std::runtime_error("Perm: index out of range");
+    }
+  }
+}
+
+Sample Perm::get(int64_t idx) const {
+  if (idx < 0 || idx >= static_cast<int64_t>(perm_.size())) {
+    throw std::out_of_range("Perm: index out of range");
+  }
+  return source_->get(perm_[idx]);
+}
+
+int64_t Perm::size() const {
+  return static_cast<int64_t>(perm_.size());
+}
+
+// ------------------------------------------------------------ dynamic batching
+namespace {
+
+// Shape of the batch that a run of samples would make (the bookkeeping of
+// mlx/data/core/BatchShape.cpp:26-66): a leading sample count over the largest
+// extents, or - with a batch dimension - extents summed along it.
+class RunShape {
+ public:
+  RunShape(bool has_dim, int dim) : has_dim_(has_dim), dim_(dim) {}
+
+  void add(const std::vector<int64_t>& shape) {
+    const int64_t nd = static_cast<int64_t>(shape.size());
+    if (!has_dim_) {
+      if (count_ == 0) {
+        shape_.assign(nd + 1, 0);
+        std::copy(shape.begin(), shape.end(), shape_.begin() + 1);
+      } else {
+        if (nd + 1 != static_cast<int64_t>(shape_.size())) {
+          throw std::runtime_error("BatchShape: batched arrays expected to have consistent shapes");
+        }
+        for (int64_t d = 0; d < nd; d++) {
+          shape_[d + 1] = std::max(shape_[d + 1], shape[d]);
+        }
+      }
+      shape_[0] += 1;
+    } else {
+      const int64_t dim = dim_ < 0 ? nd + dim_ : dim_;
+      if (dim >= nd) {
+        throw std::runtime_error("BatchShape: dimension out of bound");
+      }
+      if (count_ == 0) {
+        shape_ = shape;
+      } else {
+        if (nd != static_cast<int64_t>(shape_.size())) {
+          throw std::runtime_error("BatchShape: batched arrays expected to have consistent shapes");
+        }
+        for (int64_t d = 0; d < nd; d++) {
+          shape_[d] = d == dim ? shape_[d] + shape[d] : std::max(shape_[d], shape[d]);
+        }
+      }
+    }
+    count_++;
+  }
+
+  int64_t elements() const {
+    int64_t n = 1;
+    for (auto d : shape_) {
+      n *= d;
+    }
+    return n;
+  }
+
+  int64_t count() const { return count_; }
+
+  void clear() {
+    shape_.clear();
+    count_ = 0;
+  }
+
+ private:
+  bool has_dim_;
+  int dim_;
+  std::vector<int64_t> shape_;
+  int64_t count_ = 0;
+};
+
+} // namespace
+
+DynamicGroups dynamic_groups(
+    const std::vector<std::vector<int64_t>>& shapes, int64_t min_data_size, int64_t max_data_size,
+    bool has_batch_dim, int batch_dim, bool drop_outliers) {
+  const int64_t n = static_cast<int64_t>(shapes.size());
+  std::vector<int64_t> elements(n, 0);
+  for (int64_t i = 0; i < n; i++) {
+    if (!shapes[i].empty()) {
+      int64_t e = 1;
+      for (auto d : shapes[i]) {
+        e *= d;
+      }
+      elements[i] = e;
+    }
+  }
+  std::vector<int64_t> sorted(n);
+  for (int64_t i = 0; i < n; i++) {
+    sorted[i] = i;
+  }
+  if (max_data_size > 0) {
+    std::stable_sort(sorted.begin(), sorted.end(), [&](int64_t a, int64_t b) { return elements[a] < elements[b]; });
+  }
+
+  DynamicGroups out;
+  out.order.reserve(n);
+  RunShape run(has_batch_dim, batch_dim);
+  // the run ends at position `last` of the sorted order and holds `count` samples
+  auto accept = [&](int64_t last, int64_t count) {
+    out.batch_sizes.push_back(count);
+    out.order.insert(out.order.end(), sorted.begin() + (last + 1 - count), sorted.begin() + (last + 1));
+    run.clear();
+  };
+  auto skip = [&](int64_t last, int64_t count) {
+    out.skipped.insert(out.skipped.end(), sorted.begin() + (last + 1 - count), sorted.begin() + (last + 1));
+    run.clear();
+  };
+  const bool has_min = min_data_size > 0;
+  const bool has_max = max_data_size > 0;
+  for (int64_t i = 0; i < n; i++) {
+    run.add(shapes[sorted[i]]);
+    const int64_t size = run.elements();
+    if (has_min && size >= min_data_size && has_max && size <= max_data_size) {
+      accept(i, run.count());
+      continue;
+    }
+    if (has_max && size > max_data_size) {
+      if (run.count() == 1) {
+        // a single sample over the limit: kept as a batch of one unless outliers are dropped
+        if (!drop_outliers) {
+          accept(i, 1);
+        } else {
+          run.clear();
+        }
+        continue;
+      }
+      if (has_min) {
+        // too small before this sample, too large with it: leave the run out
+        skip(i, run.count());
+      } else {
+        // close the run before this sample and start the next one with it
+        accept(i - 1, run.count() - 1);
+        run.add(shapes[sorted[i]]);
+      }
+    }
+  }
+  if (run.count() > 0) {
+    const int64_t size = run.elements();
+    if ((!has_min || size >= min_data_size) && (!has_max || size <= max_data_size)) {
+      accept(n - 1, run.count());
+    } else {
+      skip(n - 1, run.count());
+    }
+  }
+  return out;
+}
+
+std::shared_ptr<Buffer> dynamic_batch(
+    const std::shared_ptr<Buffer>& source, const std::shared_ptr<Buffer>& size_source, const std::string& key,
+    int64_t min_data_size, int64_t max_data_size, const std::unordered_map<std::string, double>& pad_values,
+    const std::unordered_map<std::string, int>& batch_dims, bool drop_outliers) {
+  const int64_t n = source->size();
+  if (size_source && size_source->size() != n) {
+    throw std::runtime_error("DynamicBatch: buffer and reference size buffer do not match in size");
+  }
+  std::vector<std::vector<int64_t>> shapes(n);
+  for (int64_t i = 0; i < n; i++) {
+    if (size_source) {
+      auto arr = sample::check_key(size_source->get(i), key, ArrayType::Int64);
+      const int64_t* v = arr->data<int64_t>();
+      shapes[i].assign(v, v + arr->size());
+    } else {
+      shapes[i] = sample::check_key(source->get(i), key, ArrayType::Any)->shape();
+    }
+  }
+  const auto dim = batch_dims.find(key);
+  const DynamicGroups g = dynamic_groups(
+      shapes, min_data_size, max_data_size, dim != batch_dims.end(), dim != batch_dims.end() ? dim->second : 0,
+      drop_outliers);
+  // keep the image ops on top of the permutation, where Batch can fuse them
+  std::vector<std::shared_ptr<op::ImageTransformOp>> ops;
+  std::shared_ptr<Buffer> top = std::make_shared<Perm>(peel_image_ops(source, ops), g.order);
+  if (!ops.empty()) {
+    std::vector<std::shared_ptr<op::Op>> generic(ops.begin(), ops.end());
+    top = std::make_shared<Transform>(top, generic);
+  }
+  return std::make_shared<Batch>(top, g.batch_sizes, pad_values, batch_dims);
+}
+
 } // namespace buffer
 } // namespace data
 } // namespace mlx

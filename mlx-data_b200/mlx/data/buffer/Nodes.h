@@ -82,6 +82,40 @@ class Partition : public Buffer {
   int64_t num_partitions_, partition_, size_;
 };
 
+// The samples of `source` listed in `perm`, in that order.
+class Perm : public Buffer {
+ public:
+  Perm(const std::shared_ptr<Buffer>& source, const std::vector<int64_t>& perm);
+  Sample get(int64_t idx) const override;
+  int64_t size() const override;
+
+ private:
+  std::shared_ptr<Buffer> source_;
+  std::vector<int64_t> perm_;
+};
+
+// Size-aware grouping of mlx/data/buffer/DynamicBatch.cpp:68-207: samples are
+// ordered by the element count of `key` (stable; only when max_data_size > 0)
+// and cut into runs whose padded batch - largest extent per dimension times
+// the sample count, or the summed extent along batch_dims[key] - holds between
+// min_data_size and max_data_size elements.  Returns the accepted samples in
+// batch order, the size of every batch and the samples left out.
+struct DynamicGroups {
+  std::vector<int64_t> order;
+  std::vector<int64_t> batch_sizes;
+  std::vector<int64_t> skipped;
+};
+DynamicGroups dynamic_groups(
+    const std::vector<std::vector<int64_t>>& shapes, int64_t min_data_size, int64_t max_data_size,
+    bool has_batch_dim, int batch_dim, bool drop_outliers);
+
+// source.dynamic_batch(...): the shapes come from `size_source` (int64 arrays
+// under `key`) when given, else from the samples themselves.
+std::shared_ptr<Buffer> dynamic_batch(
+    const std::shared_ptr<Buffer>& source, const std::shared_ptr<Buffer>& size_source, const std::string& key,
+    int64_t min_data_size, int64_t max_data_size, const std::unordered_map<std::string, double>& pad_values,
+    const std::unordered_map<std::string, int>& batch_dims, bool drop_outliers);
+
 // Split a chain "source -> Transform(image op) -> ... -> Transform(image op)"
 // into its non-image base and the list of image ops above it.
 std::shared_ptr<Buffer> peel_image_ops(

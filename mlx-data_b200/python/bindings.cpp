@@ -415,6 +415,21 @@ PYBIND11_MODULE(_c, m) {
            py::arg("batch_size"), py::arg("pad") = MapD(), py::arg("dim") = MapI(),
            "Batch consecutive samples; ``batch_size`` is an int or a list of sizes. Arrays are padded "
            "to the largest shape in the batch with ``pad[key]`` (default 0).")
+      .def("dynamic_batch",
+           [](const Buffer& b, const std::string& key, const std::optional<Buffer>& size_buffer, int64_t min_data_size,
+              int64_t max_data_size, const MapD& pad, const MapI& dim, bool drop_outliers) {
+             py::gil_scoped_release release;
+             if (size_buffer) {
+               return b.dynamic_batch(*size_buffer, key, min_data_size, max_data_size, pad, dim, drop_outliers);
+             }
+             return b.dynamic_batch(key, min_data_size, max_data_size, pad, dim, drop_outliers);
+           },
+           py::arg("key"), py::kw_only(), py::arg("size_buffer") = py::none(), py::arg("min_data_size") = -1,
+           py::arg("max_data_size") = -1, py::arg("pad") = MapD(), py::arg("dim") = MapI(),
+           py::arg("drop_outliers") = false,
+           "Batches with about the same number of elements of ``key`` after padding: samples are sorted by "
+           "size and grouped so that every padded batch holds between ``min_data_size`` and ``max_data_size`` "
+           "elements.")
       .def("ordered_prefetch", &Buffer::ordered_prefetch, nogil(), py::arg("prefetch_size"), py::arg("num_thread"),
            "Fetch samples in background threads, returning them in buffer order.")
       .def("partition", &Buffer::partition, nogil(), py::arg("num_partitions"), py::arg("partition"))

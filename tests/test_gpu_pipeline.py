@@ -195,3 +195,34 @@ def test_pinned_sources_are_gathered(pkg):
     moved = s1["h2d_bytes"] - s0["h2d_bytes"]
     # a 61 x 45 window (plus filter margin) of images of at least 90 x 70 pixels
     assert 0 < moved < 0.8 * full, (moved, full)
+
+
+def test_dynamic_batch_of_images(pkg):
+    """Size-sorted batches of ragged images (the padding blow-up of plain batching
+    on mixed sizes): same batches as the reference, ops fused below the batch."""
+    ref = refpipe.reference_module()
+    if ref is None:
+        pytest.skip("needs the reference compiled under oracle/_ref")
+    rng = np.random.default_rng(8)
+    samples = []
+    for i in range(23):
+        h, w = int(rng.integers(20, 140)), int(rng.integers(20, 140))
+        samples.append({"image": rng.integers(0, 256, (h, w, 3), dtype=np.uint8), "id": np.int64(i)})
+
+    def chain(dx):
+        return (dx.buffer_from_vector(samples)
+                .image_resize_smallest_side("image", 32)
+                .dynamic_batch("image", max_data_size=6 * 32 * 64 * 3, pad={"image": 3.0}))
+
+    want = [dict(b) for b in chain(ref)]
+    got_buf = chain(pkg).key_cast("image")
+    got = [dict(got_buf[i]) for i in range(len(got_buf))]
+    assert len(got) == len(want)
+    for g, w in zip(got, want):
+        assert np.array_equal(np.asarray(g["id"]), np.asarray(w["id"]))
+        a = np.asarray(g["image"])
+        b = np.asarray(w["image"]).astype("float32") / 255
+        assert a.shape == b.shape and a.dtype == np.float32
+        d = np.abs(a.astype(np.float64) - b.astype(np.float64))
+        assert d.max() <= 1.0001 / 255
+        assert (a != b).mean() <= RESIZE_MISMATCH_MAX
