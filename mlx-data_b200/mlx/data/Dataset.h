@@ -12,6 +12,7 @@
 #include "mlx/data/Array.h"
 #include "mlx/data/Sample.h"
 #include "mlx/data/op/ImageTransform.h"
+#include "mlx/data/op/Pad.h"
 #include "mlx/data/op/KeyTransform.h"
 #include "mlx/data/op/Op.h"
 
@@ -92,6 +93,32 @@ class Dataset {
   T image_rotate_if(bool cond, const std::string& ikey, double angle, bool crop = false,
                     const std::string& okey = "", const std::string& angle_key = "") const {
     MLXD_IF_TWIN(image_rotate, ikey, angle, crop, okey, angle_key);
+  }
+
+  T pad(const std::string& ikey, int dim, int64_t lpad, int64_t rpad, double pad_value, const std::string& okey = "") const {
+    return add_(std::make_shared<op::Pad>(ikey, dim, lpad, rpad, pad_value, okey));
+  }
+  T pad_if(bool cond, const std::string& ikey, int dim, int64_t lpad, int64_t rpad, double pad_value,
+           const std::string& okey = "") const {
+    MLXD_IF_TWIN(pad, ikey, dim, lpad, rpad, pad_value, okey);
+  }
+
+  T pad_to_multiple(const std::string& ikey, int dim, int64_t pad_multiple, double pad_value,
+                    const std::string& okey = "") const {
+    return add_(std::make_shared<op::PadToMultiple>(ikey, dim, pad_multiple, pad_value, okey));
+  }
+  T pad_to_multiple_if(bool cond, const std::string& ikey, int dim, int64_t pad_multiple, double pad_value,
+                       const std::string& okey = "") const {
+    MLXD_IF_TWIN(pad_to_multiple, ikey, dim, pad_multiple, pad_value, okey);
+  }
+
+  T pad_to_size(const std::string& ikey, int dim, const std::vector<int64_t>& sizes, double pad_value,
+                const std::string& okey = "") const {
+    return add_(std::make_shared<op::PadToSize>(ikey, dim, sizes, pad_value, okey));
+  }
+  T pad_to_size_if(bool cond, const std::string& ikey, int dim, const std::vector<int64_t>& sizes, double pad_value,
+                   const std::string& okey = "") const {
+    MLXD_IF_TWIN(pad_to_size, ikey, dim, sizes, pad_value, okey);
   }
 
   T key_transform(const std::string& ikey, op::KeyTransform::Fn fn, const std::string& okey = "") const {

@@ -223,6 +223,40 @@ template <class T, class PyClass>
 void bind_ops(PyClass& c) {
   using nogil = py::call_guard<py::gil_scoped_release>;
   const char* okd = "output_key";
+  c.def("pad", &T::pad, nogil(), py::arg("key"), py::arg("dim"), py::arg("lpad"), py::arg("rpad"),
+        py::arg("pad_value"), py::arg(okd) = "", "Pad the array at ``key`` along ``dim`` on both sides.");
+  c.def("pad_if", &T::pad_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("dim"), py::arg("lpad"),
+        py::arg("rpad"), py::arg("pad_value"), py::arg(okd) = "");
+  c.def("pad_to_multiple", &T::pad_to_multiple, nogil(), py::arg("key"), py::arg("dim"), py::arg("pad_multiple"),
+        py::arg("pad_value"), py::arg(okd) = "", "Pad the end of ``dim`` up to a multiple of ``pad_multiple``.");
+  c.def("pad_to_multiple_if", &T::pad_to_multiple_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("dim"),
+        py::arg("pad_multiple"), py::arg("pad_value"), py::arg(okd) = "");
+  c.def("pad_to_size",
+        [](const T& self, const std::string& key, int dim, py::object size, double pad_value, const std::string& okey) {
+          std::vector<int64_t> sizes;
+          if (py::isinstance<py::int_>(size)) {
+            sizes.push_back(size.cast<int64_t>());
+          } else {
+            sizes = size.cast<std::vector<int64_t>>();
+          }
+          py::gil_scoped_release release;
+          return self.pad_to_size(key, dim, sizes, pad_value, okey);
+        },
+        py::arg("key"), py::arg("dim"), py::arg("size"), py::arg("pad_value"), py::arg(okd) = "",
+        "Pad the end of ``dim`` up to ``size`` (or the nearest larger entry of a list of sizes).");
+  c.def("pad_to_size_if",
+        [](const T& self, bool cond, const std::string& key, int dim, py::object size, double pad_value,
+           const std::string& okey) {
+          std::vector<int64_t> sizes;
+          if (py::isinstance<py::int_>(size)) {
+            sizes.push_back(size.cast<int64_t>());
+          } else {
+            sizes = size.cast<std::vector<int64_t>>();
+          }
+          py::gil_scoped_release release;
+          return self.pad_to_size_if(cond, key, dim, sizes, pad_value, okey);
+        },
+        py::arg("cond"), py::arg("key"), py::arg("dim"), py::arg("size"), py::arg("pad_value"), py::arg(okd) = "");
   c.def("image_center_crop", &T::image_center_crop, nogil(), py::arg("key"), py::arg("w"), py::arg("h"),
         py::arg(okd) = "", "Center crop the image at ``key`` to ``w`` x ``h``.");
   c.def("image_center_crop_if", &T::image_center_crop_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("w"),
