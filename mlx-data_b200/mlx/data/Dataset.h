@@ -13,6 +13,7 @@
 #include "mlx/data/Sample.h"
 #include "mlx/data/op/ImageTransform.h"
 #include "mlx/data/op/Pad.h"
+#include "mlx/data/op/Slice.h"
 #include "mlx/data/op/KeyTransform.h"
 #include "mlx/data/op/Op.h"
 
@@ -119,6 +120,24 @@ class Dataset {
   T pad_to_size_if(bool cond, const std::string& ikey, int dim, const std::vector<int64_t>& sizes, double pad_value,
                    const std::string& okey = "") const {
     MLXD_IF_TWIN(pad_to_size, ikey, dim, sizes, pad_value, okey);
+  }
+
+  T slice(const std::string& ikey, std::vector<int> dims, std::vector<int64_t> starts, std::vector<int64_t> ends,
+          const std::string& okey = "") const {
+    return add_(std::make_shared<op::Slice>(ikey, std::move(dims), std::move(starts), std::move(ends), okey));
+  }
+  T slice_if(bool cond, const std::string& ikey, std::vector<int> dims, std::vector<int64_t> starts,
+             std::vector<int64_t> ends, const std::string& okey = "") const {
+    MLXD_IF_TWIN(slice, ikey, std::move(dims), std::move(starts), std::move(ends), okey);
+  }
+
+  T random_slice(const std::string& ikey, std::vector<int> dims, std::vector<int64_t> sizes,
+                 const std::string& okey = "") const {
+    return add_(std::make_shared<op::RandomSlice>(ikey, std::move(dims), std::move(sizes), okey));
+  }
+  T random_slice_if(bool cond, const std::string& ikey, std::vector<int> dims, std::vector<int64_t> sizes,
+                    const std::string& okey = "") const {
+    MLXD_IF_TWIN(random_slice, ikey, std::move(dims), std::move(sizes), okey);
   }
 
   T key_transform(const std::string& ikey, op::KeyTransform::Fn fn, const std::string& okey = "") const {

@@ -223,6 +223,35 @@ template <class T, class PyClass>
 void bind_ops(PyClass& c) {
   using nogil = py::call_guard<py::gil_scoped_release>;
   const char* okd = "output_key";
+  // an int or a list of ints
+  auto ints = [](py::object o) {
+    std::vector<int64_t> v;
+    if (py::isinstance<py::int_>(o)) {
+      v.push_back(o.cast<int64_t>());
+    } else {
+      v = o.cast<std::vector<int64_t>>();
+    }
+    return v;
+  };
+  c.def("slice",
+        [ints](const T& self, const std::string& ikey, py::object dims, py::object starts, py::object ends,
+               const std::string& okey) {
+          const auto d = ints(dims);
+          auto s = ints(starts), e = ints(ends);
+          py::gil_scoped_release release;
+          return self.slice(ikey, std::vector<int>(d.begin(), d.end()), std::move(s), std::move(e), okey);
+        },
+        py::arg("ikey"), py::arg("dims"), py::arg("starts"), py::arg("ends"), py::arg(okd) = "",
+        "Keep ``[starts, ends)`` along ``dims`` of the array at ``ikey`` (ints or equally long lists).");
+  c.def("random_slice",
+        [ints](const T& self, const std::string& ikey, py::object dims, py::object sizes, const std::string& okey) {
+          const auto d = ints(dims);
+          auto s = ints(sizes);
+          py::gil_scoped_release release;
+          return self.random_slice(ikey, std::vector<int>(d.begin(), d.end()), std::move(s), okey);
+        },
+        py::arg("ikey"), py::arg("dims"), py::arg("sizes"), py::arg(okd) = "",
+        "Keep a window of ``sizes`` along ``dims`` at a uniformly random offset.");
   c.def("pad", &T::pad, nogil(), py::arg("key"), py::arg("dim"), py::arg("lpad"), py::arg("rpad"),
         py::arg("pad_value"), py::arg(okd) = "", "Pad the array at ``key`` along ``dim`` on both sides.");
   c.def("pad_if", &T::pad_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("dim"), py::arg("lpad"),

@@ -69,3 +69,35 @@ def test_pad_to_size_with_a_list_of_sizes(pkg):
         larger = [x for x in (8, 16, 24) if x > n]
         want = np.concatenate([s["tokens"], np.full((min(larger) - n if larger else 0,), 5, np.int64)])
         assert np.array_equal(np.asarray(buf[i]["tokens"]), want)
+
+
+SLICE_CHAINS = [
+    [("slice", dict(ikey="tokens", dims=0, starts=2, ends=11))],
+    [("slice", dict(ikey="feat", dims=[0, 1], starts=[0, 1], ends=[3, 4]))],
+    [("slice", dict(ikey="image", dims=[1, -1], starts=[1, 0], ends=[100, 2], output_key="part"))],
+    [("random_slice", dict(ikey="tokens", dims=0, sizes=4))],
+    [("random_slice", dict(ikey="image", dims=[0, 1], sizes=[3, 2])),
+     ("random_slice", dict(ikey="feat", dims=[1], sizes=[3]))],
+]
+
+
+@pytest.mark.parametrize("case", range(len(SLICE_CHAINS)))
+def test_slice_ops_match_reference(pkg, case):
+    ref = refpipe.reference_module()
+    if ref is None:
+        pytest.skip("needs the reference compiled under oracle/_ref")
+    samples = _samples()
+
+    def run(dx):
+        dx.core.set_state(11)
+        ds = dx.buffer_from_vector(samples)
+        for name, kw in SLICE_CHAINS[case]:
+            ds = getattr(ds, name)(**kw)
+        return [dict(ds[i]) for i in range(len(ds))]
+
+    want, got = run(ref), run(pkg)
+    for w, g in zip(want, got):
+        assert sorted(w) == sorted(g)
+        for k in w:
+            a, b = np.asarray(g[k]), np.asarray(w[k])
+            assert a.shape == b.shape and a.dtype == b.dtype and np.array_equal(a, b), k
