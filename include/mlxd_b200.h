@@ -161,13 +161,28 @@ MLXD_API int mlxd_ctx_set_timing(mlxd_ctx* ctx, int on);
  *    until the process exits;
  *  - the first call on a device looks up the array's device address; make
  *    that first call before any stream capture;
+ *  - every call waits on the host until the stream has drained (its small
+ *    tables are copied from fixed host storage that the next call reuses), so
+ *    the host blocks behind whatever is queued on that stream before it;
+ *  - the stream must belong to `device`; the calling thread's current device
+ *    is the same after the call as before it;
  *  - all calls share the one array, which keeps the previous call's contents
  *    (the call clears what must start at zero): two calls whose kernels can
  *    overlap on the GPU - different streams, or different host threads - race;
- *    order them on one stream. */
+ *    order them on one stream;
+ *  - the kernel's self-check word (a bounded wait that ran out, a shared-memory
+ *    bound) is read back at the start of the NEXT call on the same stream,
+ *    which then returns MLXD_ERR_DEVICE and launches nothing; after the last
+ *    call of a run ask mlxd_noalloc_status. */
 #define MLXD_NOALLOC_MAX_SAMPLES 1024
 MLXD_API int mlxd_fused_batch_noalloc(
     int device, void* cuda_stream, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch);
+
+/* Self-check word of the most recent mlxd_fused_batch_noalloc kernel on this
+ * device, read from the same fixed array (no allocation; no counterpart in the
+ * reference).  Waits for `cuda_stream`, stores the word in *status (0 = clean),
+ * clears it, and returns MLXD_ERR_DEVICE when it was set. */
+MLXD_API int mlxd_noalloc_status(int device, void* cuda_stream, int32_t* status);
 
 /* Enqueue one fused batch on a lane and return: host sources are copied to the
  * device (only the rows the chain reads), one kernel writes every slot, and a
@@ -187,6 +202,15 @@ MLXD_API int mlxd_batch_wait(mlxd_ctx* ctx, int lane, int timeout_ms);
  * stream).  Nothing is copied except the descriptors. */
 MLXD_API int mlxd_fused_batch_on_stream(
     mlxd_ctx* ctx, void* cuda_stream, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch);
+
+/* Self-check word of the kernels launched by mlxd_fused_batch_on_stream: waits
+ * for `cuda_stream`, stores the word in *status (0 = clean; bit 1/2: a pass
+ * larger than the planned shared memory, 4: a bounded wait on a bulk copy ran
+ * out, 8: more filter rows than planned), clears it, and returns
+ * MLXD_ERR_DEVICE when it was set.  The lanes of mlxd_fused_batch report the
+ * same word through mlxd_batch_wait.  No counterpart in the reference, whose
+ * CPU ops throw where they stand. */
+MLXD_API int mlxd_stream_status(mlxd_ctx* ctx, void* cuda_stream, int32_t* status);
 
 /* One entry per named op, host buffers in and out, synchronous; for chains
  * that cannot be fused (a host callback between two ops).  Each runs the same

@@ -78,6 +78,7 @@ EXPORTS = [
     "mlxd_image_crop", "mlxd_image_hflip", "mlxd_image_affine", "mlxd_image_channel_reduction",
     "mlxd_batch_pad", "mlxd_cast_scale_normalise", "mlxd_stats_get",
     "mlxd_device_alloc", "mlxd_device_free", "mlxd_ctx_set_timing", "mlxd_fused_batch_noalloc",
+    "mlxd_noalloc_status", "mlxd_stream_status",
 ]
 NOALLOC_MAX_SAMPLES = 1024
 
@@ -128,6 +129,8 @@ def load():
     lib.mlxd_device_free.restype = None
     lib.mlxd_ctx_set_timing.argtypes = [vp, i32]
     lib.mlxd_fused_batch_noalloc.argtypes = [i32, vp, vp, i32, ctypes.POINTER(BatchDesc)]
+    lib.mlxd_noalloc_status.argtypes = [i32, vp, ctypes.POINTER(ctypes.c_int32)]
+    lib.mlxd_stream_status.argtypes = [vp, vp, ctypes.POINTER(ctypes.c_int32)]
     _lib = lib
     return lib
 
@@ -171,6 +174,16 @@ def fused_batch_noalloc(device, stream, descs, batch):
         raise MlxdError(rc, lib.mlxd_last_error().decode())
 
 
+def noalloc_status(device, stream):
+    """mlxd_noalloc_status: the self-check word of the last allocation-free launch (0 = clean)."""
+    lib = load()
+    word = ctypes.c_int32(-1)
+    rc = lib.mlxd_noalloc_status(device, ctypes.c_void_p(stream), ctypes.byref(word))
+    if rc not in (OK, ERR_DEVICE):
+        raise MlxdError(rc, lib.mlxd_last_error().decode())
+    return word.value
+
+
 class Context:
     """One device, ``n_lanes`` independent lanes (see include/mlxd_b200.h)."""
 
@@ -207,6 +220,14 @@ class Context:
         assert descs.dtype == SAMPLE_DTYPE and descs.flags.c_contiguous
         self._check(self.lib.mlxd_fused_batch_on_stream(
             self.handle, ctypes.c_void_p(stream), descs.ctypes.data, len(descs), ctypes.byref(batch)))
+
+    def stream_status(self, stream):
+        """mlxd_stream_status: waits for the stream, returns the self-check word (0 = clean)."""
+        word = ctypes.c_int32(-1)
+        rc = self.lib.mlxd_stream_status(self.handle, ctypes.c_void_p(stream), ctypes.byref(word))
+        if rc not in (OK, ERR_DEVICE):
+            self._check(rc)
+        return word.value
 
     # ---- one entry per op, host buffers, synchronous ----
     def image_resize(self, img, dw, dh):

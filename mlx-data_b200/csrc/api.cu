@@ -10,6 +10,9 @@ namespace {
 
 thread_local std::string g_last;
 
+// int32 words between the self-check words of two lanes
+constexpr size_t kStatusStride = 16;
+
 void destroy_lane(Lane* l) {
   if (!l) {
     return;
@@ -110,15 +113,16 @@ int mlxd_ctx_create(int device, int n_lanes, mlxd_ctx** out) {
   if (device < 0 || device >= count) {
     return fail(MLXD_ERR_INVALID, "mlxd_ctx_create: no such CUDA device");
   }
-  MLXD_CUDA(cudaSetDevice(device));
+  MLXD_ON_DEVICE(device);
   mlxd_ctx* ctx = new (std::nothrow) mlxd_ctx();
   if (!ctx) {
     return fail(MLXD_ERR_NOMEM, "out of host memory");
   }
   ctx->device = device;
   ctx->n_user_lanes = n_lanes;
-  e = cudaMalloc(reinterpret_cast<void**>(&ctx->d_status), sizeof(int32_t));
-  if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int32_t));
+  const size_t status_bytes = (size_t)(n_lanes + 2) * kStatusStride * sizeof(int32_t);
+  e = cudaMalloc(reinterpret_cast<void**>(&ctx->d_status), status_bytes);
+  if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, status_bytes);
   if (e != cudaSuccess) {
     mlxd_ctx_destroy(ctx);
     return fail_cuda(e, "status word");
@@ -132,6 +136,7 @@ int mlxd_ctx_create(int device, int n_lanes, mlxd_ctx** out) {
       mlxd_ctx_destroy(ctx);
       return rc;
     }
+    l->d_status = ctx->d_status + (size_t)i * kStatusStride;
     ctx->lanes.push_back(l);
   }
   *out = ctx;
@@ -142,7 +147,7 @@ void mlxd_ctx_destroy(mlxd_ctx* ctx) {
   if (!ctx) {
     return;
   }
-  cudaSetDevice(ctx->device);
+  DeviceGuard on_device(ctx->device);
   for (Lane* l : ctx->lanes) {
     destroy_lane(l);
   }
@@ -193,7 +198,8 @@ void* mlxd_device_alloc(mlxd_ctx* ctx, size_t bytes) {
     return nullptr;
   }
   void* p = nullptr;
-  cudaError_t e = cudaSetDevice(ctx->device);
+  DeviceGuard on_device(ctx->device);
+  cudaError_t e = on_device.err;
   if (e == cudaSuccess) e = cudaMalloc(&p, bytes == 0 ? 1 : bytes);
   if (e != cudaSuccess) {
     fail_cuda(e, "cudaMalloc");
@@ -204,7 +210,7 @@ void* mlxd_device_alloc(mlxd_ctx* ctx, size_t bytes) {
 
 void mlxd_device_free(mlxd_ctx* ctx, void* p) {
   if (ctx && p) {
-    cudaSetDevice(ctx->device);
+    DeviceGuard on_device(ctx->device);
     cudaFree(p);
   }
 }
@@ -243,7 +249,7 @@ int mlxd_fused_batch_on_stream(
   if (batch->src_mem != MLXD_MEM_DEVICE || batch->dst_mem != MLXD_MEM_DEVICE || !batch->dst) {
     return fail(MLXD_ERR_INVALID, "mlxd_fused_batch_on_stream: sources and destination must be device memory");
   }
-  MLXD_CUDA(cudaSetDevice(ctx->device));
+  MLXD_ON_DEVICE(ctx->device);
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   // validate + plan
   std::vector<DevSample> dev;
@@ -255,6 +261,7 @@ int mlxd_fused_batch_on_stream(
   if (rc != MLXD_OK) {
     return rc;
   }
+  p.status = ring.d_status;
   rc = plan_samples(samples, n, &b, dev, need);
   if (rc != MLXD_OK) {
     return rc;
@@ -307,6 +314,28 @@ int mlxd_fused_batch_on_stream(
   ctx->batches += 1;
   ctx->samples += n;
   ctx->launches += 1;
+  return MLXD_OK;
+}
+
+int mlxd_stream_status(mlxd_ctx* ctx, void* cuda_stream, int32_t* status) {
+  if (!ctx) {
+    return fail(MLXD_ERR_INVALID, "mlxd_stream_status: null context");
+  }
+  MLXD_ON_DEVICE(ctx->device);
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  Lane& ring = *ctx->lanes[ctx->n_user_lanes + 1];
+  std::lock_guard<std::mutex> guard(ring.mu);
+  MLXD_CUDA(cudaMemcpyAsync(ring.h_status, ring.d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+  MLXD_CUDA(cudaStreamSynchronize(stream));
+  const int32_t seen = *ring.h_status;
+  if (status) {
+    *status = seen;
+  }
+  if (seen != 0) {
+    *ring.h_status = 0;
+    MLXD_CUDA(cudaMemsetAsync(ring.d_status, 0, sizeof(int32_t), stream));
+    return fail(MLXD_ERR_DEVICE, "kernel self-check failed (status " + std::to_string(seen) + ")");
+  }
   return MLXD_OK;
 }
 

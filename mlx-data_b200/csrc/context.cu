@@ -102,36 +102,41 @@ int arena_reserve(mlxd_ctx* ctx, Arena& a, size_t bytes, bool pinned, cudaStream
   return MLXD_OK;
 }
 
+// "sample <i>: <what>" as the thread's error text.  Only failing calls come
+// here, so a call that succeeds builds no string at all.
+static int bad_sample(int i, const char* what) {
+  return fail(MLXD_ERR_INVALID, "sample " + std::to_string(i) + ": " + what);
+}
+
 static int check_sample(const mlxd_sample_desc& d, int i, const mlxd_batch_desc* b, int slot_h, int slot_w) {
-  const std::string at = "sample " + std::to_string(i) + ": ";
   if (!d.src) {
-    return fail(MLXD_ERR_INVALID, at + "null source");
+    return bad_sample(i, "null source");
   }
   if (d.src_h <= 0 || d.src_w <= 0) {
-    return fail(MLXD_ERR_INVALID, at + "image: cannot create image with 0 or negative dimension");
+    return bad_sample(i, "image: cannot create image with 0 or negative dimension");
   }
   if (d.pre_w <= 0 || d.pre_h <= 0 || d.pre_x < 0 || d.pre_y < 0 ||
       (int64_t)d.pre_x + d.pre_w > d.src_w || (int64_t)d.pre_y + d.pre_h > d.src_h) {
-    return fail(MLXD_ERR_INVALID, at + "window before the geometric op leaves the source image");
+    return bad_sample(i, "window before the geometric op leaves the source image");
   }
   if (d.geom < MLXD_GEOM_NONE || d.geom > MLXD_GEOM_AFFINE) {
-    return fail(MLXD_ERR_INVALID, at + "unknown geometric op");
+    return bad_sample(i, "unknown geometric op");
   }
   if (d.geom_w <= 0 || d.geom_h <= 0) {
-    return fail(MLXD_ERR_INVALID, at + "image: cannot create image with 0 or negative dimension");
+    return bad_sample(i, "image: cannot create image with 0 or negative dimension");
   }
   if (d.geom == MLXD_GEOM_NONE && (d.geom_w != d.pre_w || d.geom_h != d.pre_h)) {
-    return fail(MLXD_ERR_INVALID, at + "geom_w, geom_h must equal pre_w, pre_h without a geometric op");
+    return bad_sample(i, "geom_w, geom_h must equal pre_w, pre_h without a geometric op");
   }
   if (d.post_w <= 0 || d.post_h <= 0 || d.post_x < 0 || d.post_y < 0 ||
       (int64_t)d.post_x + d.post_w > d.geom_w || (int64_t)d.post_y + d.post_h > d.geom_h) {
-    return fail(MLXD_ERR_INVALID, at + "window after the geometric op leaves its output");
+    return bad_sample(i, "window after the geometric op leaves its output");
   }
   if (d.post_w > slot_w || d.post_h > slot_h) {
-    return fail(MLXD_ERR_INVALID, at + "result is larger than its slot in the batch");
+    return bad_sample(i, "result is larger than its slot in the batch");
   }
   if ((int64_t)d.src_h * d.src_w * b->channels >= ((int64_t)1 << 40)) {
-    return fail(MLXD_ERR_INVALID, at + "source image too large");
+    return bad_sample(i, "source image too large");
   }
   return MLXD_OK;
 }
@@ -390,7 +395,7 @@ int prepare_launch(
   p.gray_bias = b->gray_bias;
   p.out_f32 = b->out_dtype == MLXD_F32;
   p.pad_px = (int32_t)(uint8_t)(int32_t)b->pad_value;
-  p.status = ctx->d_status;
+  p.status = ctx->d_status;   // callers point this at their lane's word
   if (p.out_f32) {
     if (!(b->divisor != 0.0f)) {
       return fail(MLXD_ERR_INVALID, "cast divisor must be non-zero");
@@ -415,7 +420,7 @@ int enqueue_on_lane(
   if (!batch->dst && !per_sample_dst) {
     return fail(MLXD_ERR_INVALID, "null batch destination");
   }
-  MLXD_CUDA(cudaSetDevice(ctx->device));
+  MLXD_ON_DEVICE(ctx->device);
   LaunchParams p;
   int rc = prepare_launch(ctx, batch, n, p);
   if (rc != MLXD_OK) {
@@ -423,6 +428,7 @@ int enqueue_on_lane(
   }
   std::vector<DevSample> dev;
   PassNeed need;
+  p.status = lane.d_status;
   rc = plan_samples(samples, n, batch, dev, need);
   if (rc != MLXD_OK) {
     return rc;
@@ -599,7 +605,7 @@ int enqueue_on_lane(
     MLXD_CUDA(cudaMemcpyAsync(batch->dst, lane.d_out.ptr, out_bytes, cudaMemcpyDeviceToHost, lane.stream));
     ctx->d2h += out_bytes;
   }
-  MLXD_CUDA(cudaMemcpyAsync(lane.h_status, ctx->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, lane.stream));
+  MLXD_CUDA(cudaMemcpyAsync(lane.h_status, lane.d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, lane.stream));
   MLXD_CUDA(cudaEventRecord(lane.done, lane.stream));
   ctx->batches += 1;
   ctx->samples += n;
@@ -627,7 +633,7 @@ void harvest_timing(mlxd_ctx* ctx, Lane& lane, int slot, bool block) {
 }
 
 int wait_lane(mlxd_ctx* ctx, Lane& lane, int timeout_ms) {
-  MLXD_CUDA(cudaSetDevice(ctx->device));
+  MLXD_ON_DEVICE(ctx->device);
   const auto start = std::chrono::steady_clock::now();
   if (timeout_ms < 0) {
     // no deadline: block in the driver instead of polling it from every lane
@@ -657,7 +663,12 @@ int wait_lane(mlxd_ctx* ctx, Lane& lane, int timeout_ms) {
     }
   }
   if (*lane.h_status != 0) {
-    return fail(MLXD_ERR_DEVICE, "kernel self-check failed (status " + std::to_string(*lane.h_status) + ")");
+    // Reported once: the word is cleared so that later batches on this lane
+    // start clean (other lanes have words of their own).
+    const int32_t seen = *lane.h_status;
+    *lane.h_status = 0;
+    cudaMemsetAsync(lane.d_status, 0, sizeof(int32_t), lane.stream);
+    return fail(MLXD_ERR_DEVICE, "kernel self-check failed (status " + std::to_string(seen) + ")");
   }
   return MLXD_OK;
 }

@@ -28,6 +28,35 @@ int fail_cuda(cudaError_t e, const char* what);
     }                                         \
   } while (0)
 
+// Makes `device` current for the life of the object and puts the caller's
+// device back afterwards: an entry point of this library never leaves the
+// calling thread on another device than it came with.
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t err = cudaSuccess;
+  explicit DeviceGuard(int device) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != device) {
+      err = cudaSetDevice(device);
+      switched = err == cudaSuccess;
+    }
+  }
+  ~DeviceGuard() {
+    if (switched) {
+      cudaSetDevice(prev);
+    }
+  }
+  DeviceGuard(const DeviceGuard&) = delete;
+  DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+
+#define MLXD_ON_DEVICE(device)                                  \
+  ::mlxd::DeviceGuard device_guard__(device);                   \
+  if (device_guard__.err != cudaSuccess) {                      \
+    return ::mlxd::fail_cuda(device_guard__.err, "cudaSetDevice"); \
+  }
+
 // Grow-only device or pinned-host buffer.
 struct Arena {
   void* ptr = nullptr;
@@ -48,6 +77,7 @@ struct Lane {
   cudaEvent_t k_end[kDescSlots] = {};
   bool k_pending[kDescSlots] = {};        // recorded, not yet added to the statistics
   int next_slot = 0;
+  int32_t* d_status = nullptr;        // this lane's word of the context's status block
   int32_t* h_status = nullptr;        // pinned copy of the device status word
   std::mutex mu;                      // one caller at a time per lane
 };
@@ -66,7 +96,7 @@ struct mlxd_ctx {
   int device = 0;
   std::vector<mlxd::Lane*> lanes;     // n_lanes user lanes + one private lane for the synchronous ops
   int n_user_lanes = 0;
-  int32_t* d_status = nullptr;
+  int32_t* d_status = nullptr;        // one self-check word per lane, 64 bytes apart
   std::mutex lut_mu;
   std::map<mlxd::LutKey, float*> luts;
   std::atomic<uint64_t> batches{0}, samples{0}, launches{0}, h2d{0}, d2h{0}, reserved{0};

@@ -10,6 +10,7 @@
 // the host.
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <cstring>
 #include <mutex>
 
@@ -58,9 +59,11 @@ extern "C" int mlxd_fused_batch_noalloc(
     return fail(MLXD_ERR_INVALID, "mlxd_fused_batch_noalloc: null descriptor or negative sample count");
   }
   if (n > kMaxSamples) {
-    return fail(
-        MLXD_ERR_INVALID, "mlxd_fused_batch_noalloc: at most " + std::to_string(kMaxSamples) +
-            " samples per call (got " + std::to_string(n) + "); split the batch or use mlxd_fused_batch_on_stream");
+    char msg[160];
+    snprintf(msg, sizeof(msg),
+             "mlxd_fused_batch_noalloc: at most %d samples per call (got %d); split the batch or use "
+             "mlxd_fused_batch_on_stream", kMaxSamples, n);
+    return fail(MLXD_ERR_INVALID, msg);
   }
   if (device < 0 || device >= kMaxDevices) {
     return fail(MLXD_ERR_INVALID, "mlxd_fused_batch_noalloc: device index out of range");
@@ -86,7 +89,7 @@ extern "C" int mlxd_fused_batch_noalloc(
   if (batch->out_dtype == MLXD_F32 && !(batch->divisor != 0.0f)) {
     return fail(MLXD_ERR_INVALID, "cast divisor must be non-zero");
   }
-  MLXD_CUDA(cudaSetDevice(device));
+  MLXD_ON_DEVICE(device);
   unsigned char* scratch = nullptr;
   int rc = scratch_for(device, &scratch);
   if (rc != MLXD_OK) {
@@ -135,8 +138,13 @@ extern "C" int mlxd_fused_batch_noalloc(
   p.u_cap = need.u_cap;
   choose_kernel(p, need);
 
-  // The scratch keeps whatever the previous call left: the status word must
-  // start at zero, the tables are overwritten up to what this call reads.
+  // The scratch keeps whatever the previous call left.  Its status word is
+  // read back first (the kernel of the previous call is ahead of this copy on
+  // the stream), then cleared; the tables are overwritten up to what this call
+  // reads.
+  static int32_t previous_status;
+  previous_status = 0;
+  MLXD_CUDA(cudaMemcpyAsync(&previous_status, scratch + kStatusOffset, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
   MLXD_CUDA(cudaMemsetAsync(scratch + kStatusOffset, 0, 256, stream));
   MLXD_CUDA(cudaMemcpyAsync(scratch, table, sizeof(DevSample) * n, cudaMemcpyHostToDevice, stream));
   if (p.out_f32) {
@@ -146,6 +154,43 @@ extern "C" int mlxd_fused_batch_noalloc(
   }
   // the host tables are reused by the next call: let the copies finish
   MLXD_CUDA(cudaStreamSynchronize(stream));
+  if (previous_status != 0) {
+    // Nothing is launched: the caller learns here that the batch written by
+    // the call before this one is not to be trusted.
+    char msg[96];
+    snprintf(msg, sizeof(msg), "the previous call's kernel failed a self-check (status %d); this call ran nothing",
+             (int)previous_status);
+    return fail(MLXD_ERR_DEVICE, msg);
+  }
   MLXD_CUDA(launch_fused_batch(p, stream));
+  return MLXD_OK;
+}
+
+extern "C" int mlxd_noalloc_status(int device, void* cuda_stream, int32_t* status) {
+  if (device < 0 || device >= kMaxDevices) {
+    return fail(MLXD_ERR_INVALID, "mlxd_noalloc_status: device index out of range");
+  }
+  MLXD_ON_DEVICE(device);
+  unsigned char* scratch = nullptr;
+  int rc = scratch_for(device, &scratch);
+  if (rc != MLXD_OK) {
+    return rc;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  static int32_t seen;
+  static std::mutex seen_mu;
+  std::lock_guard<std::mutex> g(seen_mu);
+  seen = 0;
+  MLXD_CUDA(cudaMemcpyAsync(&seen, scratch + kStatusOffset, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+  MLXD_CUDA(cudaStreamSynchronize(stream));
+  if (status) {
+    *status = seen;
+  }
+  if (seen != 0) {
+    MLXD_CUDA(cudaMemsetAsync(scratch + kStatusOffset, 0, 256, stream));
+    char msg[64];
+    snprintf(msg, sizeof(msg), "kernel self-check failed (status %d)", (int)seen);
+    return fail(MLXD_ERR_DEVICE, msg);
+  }
   return MLXD_OK;
 }

@@ -6,10 +6,9 @@ allocator calls once warm): its descriptor and cast tables live in a fixed
 array inside the library instead of memory allocated per call.  Its output
 must equal, bit for bit, what the allocating entry point
 mlxd_fused_batch_on_stream writes for the same descriptors - also on a second
-call, which finds the previous call's contents in the shared array.
-
-This file sorts last on purpose: a run that stops at the first failure has
-then already run every other test.
+call, which finds the previous call's contents in the shared array.  The
+calls must leave the device's free memory as they found it and the kernel's
+self-check word clean.
 """
 import importlib
 
@@ -56,8 +55,13 @@ def test_noalloc_matches_allocating_entry_point_twice(pkg, ctx, oracle, name):
         ctx.fused_batch_on_stream(stream, descs, bd)
         bd2 = pkg.make_batch_desc(got.data_ptr(), sh, sw, 3, mean=mean, std=std, pad_value=3.0,
                                   src_mem=capi.MEM_DEVICE, dst_mem=capi.MEM_DEVICE)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         capi.fused_batch_noalloc(0, stream, descs, bd2)
         torch.cuda.synchronize()
+        if call == 1:   # the first call may still load the kernel's code; the second finds everything in place
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
+        assert capi.noalloc_status(0, stream) == 0
         assert torch.equal(got, want), "call %d differs" % call
         assert float(want.min()) > -7.0  # every element was written
 
