@@ -8,7 +8,8 @@
 // filters horizontally - a thread takes one output column of four rows over
 // all channels - quantises, casts through the table and stores straight into
 // the batch tensor.  Copy and nearest-neighbour affine bands read their source
-// through the read-only path; pad-only bands are plain 16-byte stores.
+// through the read-only path, four pixels per thread, and store 16 bytes at a
+// time; pad-only bands are plain 16-byte stores.
 //
 // The arithmetic is that of the generic kernel in fused_batch.cu: every resize
 // output is a chain acc = fma(w_k, v_k, acc) from 0 in increasing tap order,
@@ -724,51 +725,135 @@ __device__ void resize_rows(
   }
 }
 
-// Copy (crop / flip / batch only) and nearest-neighbour affine: one thread per
-// output pixel of rows [y0, vy1) x columns [xa, xb), source bytes through the
-// read-only path.
+// Source pixel of post-window pixel (px, y) of an affine sample: coordinates in
+// the pre window, or false when it falls outside it (the output is 0 there).
+// The coordinate is built from float products and float sums, then two double
+// additions, then truncation toward zero - the evaluation order of the
+// reference expression - and no multiply-add is contracted.
+__device__ __forceinline__ bool affine_source(
+    const DevSample& s, int gx, int gy, float twh, float thh, float wh, float hh, int& sx, int& sy) {
+  const float dxf = __fsub_rn((float)(long long)gx, twh);
+  const float dyf = __fsub_rn((float)(long long)gy, thh);
+  const float fx = __fadd_rn(__fadd_rn(__fmul_rn(s.mx[0], dxf), __fmul_rn(s.mx[1], dyf)), s.mx[2]);
+  const float fy = __fadd_rn(__fadd_rn(__fmul_rn(s.mx[3], dxf), __fmul_rn(s.mx[4], dyf)), s.mx[5]);
+  const long long ax = (long long)__dadd_rn(__dadd_rn((double)fx, 0.5), (double)wh);
+  const long long ay = (long long)__dadd_rn(__dadd_rn((double)fy, 0.5), (double)hh);
+  sx = (int)ax;
+  sy = (int)ay;
+  return !(ax < 0 || ay < 0 || ax >= s.pre_w || ay >= s.pre_h);
+}
+
+// Copy (crop / flip / batch only) and nearest-neighbour affine tiles: rows
+// [y0, vy1) x columns [xa, xb) of the slot, a thread takes four adjacent pixels
+// of a row.  The cast table is read from shared memory (lut_s); the four pixels
+// leave as 16-byte stores when the row segment allows it.  Without a geometric
+// op the four source pixels are adjacent too and come as aligned words.
 template <int C>
-__device__ void gather_rows(const DevSample& s, const LaunchParams& p, int y0, int vy1, int xa, int xb) {
+__device__ void gather_rows(
+    const DevSample& s, const LaunchParams& p, unsigned lut_s, int y0, int vy1, int xa, int xb) {
   const int nvx = xb - xa;
   const int nvy = vy1 - y0;
+  const int quads = (nvx + 3) >> 2;
   float* base = reinterpret_cast<float*>(s.dst);
   const float twh = (float)((double)s.geom_w / 2.0);
   const float thh = (float)((double)s.geom_h / 2.0);
   const float wh = (float)((double)s.pre_w / 2.0);
   const float hh = (float)((double)s.pre_h / 2.0);
-  for (int ry = 0; ry < nvy; ry++) {
+  const size_t row_floats = (size_t)s.slot_w * C;
+  const bool vec_ok = (row_floats & 3) == 0 && ((xa * C) & 3) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+  // last 4-byte word of the source image: nothing behind it is read
+  const uintptr_t last_word = (reinterpret_cast<uintptr_t>(s.src) + (size_t)s.src_h * s.src_w * C - 1) & ~(uintptr_t)3;
+  for (int i = threadIdx.x; i < nvy * quads; i += kThreads) {
+    const int ry = i / quads;
+    const int q = i - ry * quads;
+    const int x_first = xa + 4 * q;
+    const int npx = min(4, xb - x_first);
     const int gy = s.post_y + y0 + ry;
-    for (int rx = threadIdx.x; rx < nvx; rx += kThreads) {
-      const int px = s.post_flip ? (s.post_w - 1 - (xa + rx)) : (xa + rx);
-      const int gx = s.post_x + px;
-      int sx = gx, sy = gy;
-      bool inside = true;
-      if (s.mode == kModeAffine) {
-        // The coordinate is built from float products and float sums, then two
-        // double additions, then truncation toward zero - the evaluation order
-        // of the reference expression - and no multiply-add is contracted.
-        const float dxf = __fsub_rn((float)(long long)gx, twh);
-        const float dyf = __fsub_rn((float)(long long)gy, thh);
-        const float fx = __fadd_rn(__fadd_rn(__fmul_rn(s.mx[0], dxf), __fmul_rn(s.mx[1], dyf)), s.mx[2]);
-        const float fy = __fadd_rn(__fadd_rn(__fmul_rn(s.mx[3], dxf), __fmul_rn(s.mx[4], dyf)), s.mx[5]);
-        const long long ax = (long long)__dadd_rn(__dadd_rn((double)fx, 0.5), (double)wh);
-        const long long ay = (long long)__dadd_rn(__dadd_rn((double)fy, 0.5), (double)hh);
-        inside = !(ax < 0 || ay < 0 || ax >= s.pre_w || ay >= s.pre_h);
-        sx = (int)ax;
-        sy = (int)ay;
-      }
-      float* dst = base + ((size_t)(y0 + ry) * s.slot_w + (xa + rx)) * C;
-      if (inside) {
+    unsigned px[4][C];   // source bytes of the four pixels
+    if (s.mode == kModeAffine) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int x = x_first + (j < npx ? j : 0);
+        const int gx = s.post_x + (s.post_flip ? (s.post_w - 1 - x) : x);
+        int sx, sy;
+        const bool inside = affine_source(s, gx, gy, twh, thh, wh, hh, sx, sy);
         const int ix = s.pre_x + (s.pre_flip ? (s.pre_w - 1 - sx) : sx);
-        const uint8_t* g = s.src + ((size_t)(s.pre_y + sy) * s.src_w + ix) * C;
+        // the pixel's C bytes from the one or two aligned words that hold them
+        const uintptr_t g = reinterpret_cast<uintptr_t>(s.src) + ((size_t)(s.pre_y + sy) * s.src_w + ix) * C;
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(g & ~(uintptr_t)3);
+        const unsigned sh = (unsigned)(g & 3) * 8u;
+        const uint32_t w0 = inside ? __ldg(w) : 0u;
+        const uint32_t w1 = (inside && (int)(g & 3) + C > 4) ? __ldg(w + 1) : 0u;
+        const uint32_t v = __funnelshift_r(w0, w1, sh);
 #pragma unroll
         for (int ch = 0; ch < C; ch++) {
-          dst[ch] = __ldg(p.lut + ch * 256 + __ldg(g + ch));
+          px[j][ch] = (v >> (8 * ch)) & 0xffu;
         }
-      } else {
+      }
+    } else {
+      // pre_flip is folded into post_flip for copies: the source pixels of columns
+      // x_first .. x_first + 3 are adjacent, ascending or (mirrored) descending
+      const int gx_a = s.post_x + (s.post_flip ? (s.post_w - 1 - x_first) : x_first);
+      const int sx_lo = s.pre_x + (s.post_flip ? gx_a - (npx - 1) : gx_a);
+      const uintptr_t g =
+          reinterpret_cast<uintptr_t>(s.src) + ((size_t)(s.pre_y + gy) * s.src_w + sx_lo) * C;
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(g & ~(uintptr_t)3);
+      const unsigned sh = (unsigned)(g & 3) * 8u;
+      const int need = (int)(g & 3) + npx * C;   // bytes from the first word on
+      uint32_t x[C + 1];
+#pragma unroll
+      for (int k = 0; k < C + 1; k++) {
+        const bool take = 4 * k < need && reinterpret_cast<uintptr_t>(w + k) <= last_word;
+        x[k] = take ? __ldg(w + k) : 0u;
+      }
+      uint32_t v[C];   // the 4 * C bytes from g on
+#pragma unroll
+      for (int k = 0; k < C; k++) {
+        v[k] = __funnelshift_r(x[k], x[k + 1], sh);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
 #pragma unroll
         for (int ch = 0; ch < C; ch++) {
-          dst[ch] = __ldg(p.lut + ch * 256);
+          const int byte = j * C + ch;
+          const unsigned val = (v[byte >> 2] >> (8 * (byte & 3))) & 0xffu;
+          // mirrored: source pixel j is output pixel npx - 1 - j
+          if (!s.post_flip) {
+            px[j][ch] = val;
+          } else {
+#pragma unroll
+            for (int o = 0; o < 4; o++) {
+              if (o == npx - 1 - j) {
+                px[o][ch] = val;
+              }
+            }
+          }
+        }
+      }
+    }
+    float out[4][C];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+#pragma unroll
+      for (int ch = 0; ch < C; ch++) {
+        out[j][ch] = __uint_as_float(lds_u32<0>(lut_s + (unsigned)ch * 1024u + 4u * px[j][ch]));
+      }
+    }
+    float* dst = base + ((size_t)(y0 + ry) * s.slot_w + x_first) * C;
+    if (vec_ok && npx == 4) {
+      const float* o = &out[0][0];
+#pragma unroll
+      for (int k = 0; k < C; k++) {
+        reinterpret_cast<float4*>(dst)[k] = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        if (j < npx) {
+#pragma unroll
+          for (int ch = 0; ch < C; ch++) {
+            dst[j * C + ch] = out[j][ch];
+          }
         }
       }
     }
@@ -807,15 +892,15 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
     fill_rect_f32<C>(out, s.slot_w, y0, y1, x0, x1, padf);
     return;
   }
+  Smem sm;
+  smem_layout(p, smem_addr(smem_raw), &sm);
+  for (int i = threadIdx.x; i < C * 256; i += kThreads) {
+    sp<float>(sm.lut)[i] = __ldg(p.lut + i);
+  }
   if (s.mode == kModeResize) {
-    Smem sm;
-    smem_layout(p, smem_addr(smem_raw), &sm);
     if (threadIdx.x == 0) {
       mbar_init(sm.bar, 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    for (int i = threadIdx.x; i < C * 256; i += kThreads) {
-      sp<float>(sm.lut)[i] = __ldg(p.lut + i);
     }
     __syncthreads();
     int gx_lo, gx_hi;
@@ -832,7 +917,8 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
       resize_rows<C>(s, p, sm, parity, first_use, by, min(s.sub_h, s.post_y + vy1 - by), gx_lo, gx_hi);
     }
   } else {
-    gather_rows<C>(s, p, y0, vy1, x0, vx1);
+    __syncthreads();
+    gather_rows<C>(s, p, sm.lut, y0, vy1, x0, vx1);
   }
   // pad the part of the band outside the post window
   fill_rect_f32<C>(out, s.slot_w, vy1, y1, x0, x1, padf);
@@ -853,10 +939,7 @@ __global__ void __launch_bounds__(kThreads, 3) fused_fast_kernel(const LaunchPar
 } // namespace
 
 size_t fused_fast_smem_bytes(const LaunchParams& p) {
-  if (p.src_tile_bytes == 0) {
-    return 0;   // no sample resizes: nothing is staged
-  }
-  return smem_layout(p, 0u, nullptr);
+  return smem_layout(p, 0u, nullptr);   // without a resize in the launch only the cast table
 }
 
 cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
