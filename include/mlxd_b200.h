@@ -108,6 +108,9 @@ typedef struct mlxd_stats {
   uint64_t timed_launches;        /* launches included in kernel_ns; 0 unless timing is on */
   uint64_t algo_src_bytes;        /* summed source footprints: the uint8 source rectangle each sample's chain can read */
   uint64_t algo_dst_bytes;        /* summed batch tensor bytes written, padding included */
+  uint64_t h2d_ns;                /* timed launches: device time of the host-to-device stage (gather kernel or copies) */
+  uint64_t d2h_ns;                /* timed launches: device time of the batch's copy back to the host */
+  uint64_t host_stage_ns;         /* host time spent copying sources from ordinary memory into page-locked blocks */
 } mlxd_stats;
 
 /* Context: one device, n_lanes independent lanes.  A lane owns a CUDA stream, a

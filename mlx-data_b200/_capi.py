@@ -58,7 +58,7 @@ class BatchDesc(ctypes.Structure):
 class Stats(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint64) for n in (
         "batches", "samples", "kernel_launches", "h2d_bytes", "d2h_bytes", "device_bytes_reserved",
-        "kernel_ns", "timed_launches", "algo_src_bytes", "algo_dst_bytes")]
+        "kernel_ns", "timed_launches", "algo_src_bytes", "algo_dst_bytes", "h2d_ns", "d2h_ns", "host_stage_ns")]
 
 
 # numpy mirror of SampleDesc so a whole batch of descriptors is one array

@@ -26,7 +26,11 @@ void destroy_lane(Lane* l) {
     if (l->desc_copied[s]) cudaEventDestroy(l->desc_copied[s]);
     if (l->k_begin[s]) cudaEventDestroy(l->k_begin[s]);
     if (l->k_end[s]) cudaEventDestroy(l->k_end[s]);
+    if (l->in_begin[s]) cudaEventDestroy(l->in_begin[s]);
+    if (l->out_end[s]) cudaEventDestroy(l->out_end[s]);
   }
+  if (l->src_copied) cudaEventDestroy(l->src_copied);
+  if (l->h_src.ptr) cudaFreeHost(l->h_src.ptr);
   if (l->d_src.ptr) cudaFree(l->d_src.ptr);
   if (l->d_out.ptr) cudaFree(l->d_out.ptr);
   if (l->h_status) cudaFreeHost(l->h_status);
@@ -42,10 +46,13 @@ int make_lane(Lane** out) {
   }
   cudaError_t e = cudaStreamCreateWithFlags(&l->stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&l->done, cudaEventDisableTiming | cudaEventBlockingSync);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&l->src_copied, cudaEventDisableTiming);
   for (int s = 0; s < kDescSlots && e == cudaSuccess; s++) {
     e = cudaEventCreateWithFlags(&l->desc_copied[s], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreate(&l->k_begin[s]);
     if (e == cudaSuccess) e = cudaEventCreate(&l->k_end[s]);
+    if (e == cudaSuccess) e = cudaEventCreate(&l->in_begin[s]);
+    if (e == cudaSuccess) e = cudaEventCreate(&l->out_end[s]);
   }
   if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&l->h_status), sizeof(int32_t), cudaHostAllocDefault);
   if (e != cudaSuccess) {
@@ -493,6 +500,9 @@ int mlxd_stats_get(mlxd_ctx* ctx, mlxd_stats* out) {
   out->h2d_bytes = ctx->h2d.load();
   out->d2h_bytes = ctx->d2h.load();
   out->device_bytes_reserved = ctx->reserved.load();
+  out->h2d_ns = ctx->h2d_ns.load();
+  out->d2h_ns = ctx->d2h_ns.load();
+  out->host_stage_ns = ctx->host_stage_ns.load();
   return MLXD_OK;
 }
 

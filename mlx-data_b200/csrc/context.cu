@@ -498,8 +498,12 @@ int enqueue_on_lane(
       gather = src_dev[i] != nullptr;
     }
   }
+  bool bounce = false;              // some source lies in ordinary (pageable) host memory
+  std::vector<char> direct_copy;    // per sample: page-locked memory the copy engines can read
+  unsigned int host_flags = 0;
   if (host_src) {
     pieces.resize(n);
+    direct_copy.assign(n, 0);
     for (int i = 0; i < n; i++) {
       int32_t r0, r1, c0, c1;
       needed_region(dev[i], 2, r0, r1, c0, c1);
@@ -510,10 +514,18 @@ int enqueue_on_lane(
         const char* v = std::getenv("MLXD_TRIM_PERCENT");
         return v && *v ? std::atoi(v) : 60;
       }();
-      if (!gather && (int64_t)(dev[i].src_w - (c1 - c0)) * 100 < (int64_t)trim_percent * dev[i].src_w) {
+      // (sources in ordinary host memory are packed by the calling thread into a
+      // page-locked block, which drops the columns for free)
+      const bool direct = !gather && cudaHostGetFlags(&host_flags, const_cast<uint8_t*>(samples[i].src)) == cudaSuccess;
+      if (!gather && !direct) {
+        cudaGetLastError();
+        bounce = true;
+      }
+      if (direct && (int64_t)(dev[i].src_w - (c1 - c0)) * 100 < (int64_t)trim_percent * dev[i].src_w) {
         c0 = 0;
         c1 = dev[i].src_w;
       }
+      direct_copy[i] = direct;
       // The staged block is an image of its own: rows [r0, r1), columns
       // [c0, c1) of the source, tightly packed.
       pieces[i].offset = stage_bytes;
@@ -567,6 +579,40 @@ int enqueue_on_lane(
   }
   MLXD_CUDA(cudaMemcpyAsync(lane.d_desc[slot].ptr, lane.h_desc[slot].ptr, upload, cudaMemcpyHostToDevice, lane.stream));
   MLXD_CUDA(cudaEventRecord(lane.desc_copied[slot], lane.stream));
+  const bool timed = ctx->timing.load() != 0;
+  lane.in_timed[slot] = false;
+  lane.out_timed[slot] = false;
+  if (bounce) {
+    // Pack the rectangles of the pageable sources into the lane's page-locked
+    // block (the calling thread does the copying), then one copy for all of
+    // them.  The block may still be feeding the previous batch of this lane.
+    rc = arena_reserve(ctx, lane.h_src, stage_bytes + 256, true, lane.stream);
+    if (rc != MLXD_OK) {
+      return rc;
+    }
+    MLXD_CUDA(cudaEventSynchronize(lane.src_copied));
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int i = 0; i < n; i++) {
+      if (direct_copy[i]) {
+        continue;
+      }
+      uint8_t* to = static_cast<uint8_t*>(lane.h_src.ptr) + pieces[i].offset;
+      const uint8_t* from = pieces[i].from;
+      if (pieces[i].row_bytes == pieces[i].from_pitch) {
+        std::memcpy(to, from, pieces[i].row_bytes * pieces[i].rows);
+      } else {
+        for (size_t r = 0; r < pieces[i].rows; r++) {
+          std::memcpy(to + r * pieces[i].row_bytes, from + r * pieces[i].from_pitch, pieces[i].row_bytes);
+        }
+      }
+    }
+    ctx->host_stage_ns += (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(
+        std::chrono::steady_clock::now() - t0).count();
+  }
+  if (timed && host_src) {
+    MLXD_CUDA(cudaEventRecord(lane.in_begin[slot], lane.stream));
+    lane.in_timed[slot] = true;
+  }
   if (gather) {
     const GatherPiece* gd =
         reinterpret_cast<const GatherPiece*>(static_cast<const uint8_t*>(lane.d_desc[slot].ptr) + desc_bytes);
@@ -578,21 +624,34 @@ int enqueue_on_lane(
     }
     ctx->h2d += moved;
   } else if (host_src) {
+    bool all_bounced = true;
     for (int i = 0; i < n; i++) {
-      uint8_t* to = static_cast<uint8_t*>(lane.d_src.ptr) + pieces[i].offset;
-      if (pieces[i].row_bytes == pieces[i].from_pitch) {
-        MLXD_CUDA(cudaMemcpyAsync(
-            to, pieces[i].from, pieces[i].row_bytes * pieces[i].rows, cudaMemcpyHostToDevice, lane.stream));
-      } else {
-        MLXD_CUDA(cudaMemcpy2DAsync(
-            to, pieces[i].row_bytes, pieces[i].from, pieces[i].from_pitch, pieces[i].row_bytes, pieces[i].rows,
-            cudaMemcpyHostToDevice, lane.stream));
+      all_bounced = all_bounced && !direct_copy[i];
+    }
+    if (all_bounced) {
+      MLXD_CUDA(cudaMemcpyAsync(lane.d_src.ptr, lane.h_src.ptr, stage_bytes, cudaMemcpyHostToDevice, lane.stream));
+    } else {
+      for (int i = 0; i < n; i++) {
+        uint8_t* to = static_cast<uint8_t*>(lane.d_src.ptr) + pieces[i].offset;
+        const size_t bytes = pieces[i].row_bytes * pieces[i].rows;
+        if (!direct_copy[i]) {
+          MLXD_CUDA(cudaMemcpyAsync(
+              to, static_cast<uint8_t*>(lane.h_src.ptr) + pieces[i].offset, bytes, cudaMemcpyHostToDevice, lane.stream));
+        } else if (pieces[i].row_bytes == pieces[i].from_pitch) {
+          MLXD_CUDA(cudaMemcpyAsync(to, pieces[i].from, bytes, cudaMemcpyHostToDevice, lane.stream));
+        } else {
+          MLXD_CUDA(cudaMemcpy2DAsync(
+              to, pieces[i].row_bytes, pieces[i].from, pieces[i].from_pitch, pieces[i].row_bytes, pieces[i].rows,
+              cudaMemcpyHostToDevice, lane.stream));
+        }
       }
+    }
+    if (bounce) {
+      MLXD_CUDA(cudaEventRecord(lane.src_copied, lane.stream));
     }
     ctx->h2d += stage_bytes;
   }
   p.samples = static_cast<const DevSample*>(lane.d_desc[slot].ptr);
-  const bool timed = ctx->timing.load() != 0;
   if (timed) {
     MLXD_CUDA(cudaEventRecord(lane.k_begin[slot], lane.stream));
   }
@@ -604,6 +663,10 @@ int enqueue_on_lane(
   if (host_dst) {
     MLXD_CUDA(cudaMemcpyAsync(batch->dst, lane.d_out.ptr, out_bytes, cudaMemcpyDeviceToHost, lane.stream));
     ctx->d2h += out_bytes;
+    if (timed) {
+      MLXD_CUDA(cudaEventRecord(lane.out_end[slot], lane.stream));
+      lane.out_timed[slot] = true;
+    }
   }
   MLXD_CUDA(cudaMemcpyAsync(lane.h_status, lane.d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, lane.stream));
   MLXD_CUDA(cudaEventRecord(lane.done, lane.stream));
@@ -624,11 +687,25 @@ void harvest_timing(mlxd_ctx* ctx, Lane& lane, int slot, bool block) {
   } else if (cudaEventQuery(lane.k_end[slot]) != cudaSuccess) {
     return;
   }
+  if (lane.out_timed[slot]) {
+    const cudaError_t oe = block ? cudaEventSynchronize(lane.out_end[slot]) : cudaEventQuery(lane.out_end[slot]);
+    if (oe != cudaSuccess) {
+      return;
+    }
+  }
   float ms = 0.0f;
   if (cudaEventElapsedTime(&ms, lane.k_begin[slot], lane.k_end[slot]) == cudaSuccess) {
     ctx->kernel_ns += (uint64_t)((double)ms * 1e6);
     ctx->timed_launches += 1;
   }
+  if (lane.in_timed[slot] && cudaEventElapsedTime(&ms, lane.in_begin[slot], lane.k_begin[slot]) == cudaSuccess) {
+    ctx->h2d_ns += (uint64_t)((double)ms * 1e6);
+  }
+  if (lane.out_timed[slot] && cudaEventElapsedTime(&ms, lane.k_end[slot], lane.out_end[slot]) == cudaSuccess) {
+    ctx->d2h_ns += (uint64_t)((double)ms * 1e6);
+  }
+  lane.in_timed[slot] = false;
+  lane.out_timed[slot] = false;
   lane.k_pending[slot] = false;
 }
 

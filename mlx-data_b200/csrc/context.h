@@ -69,13 +69,19 @@ struct Lane {
   cudaStream_t stream = nullptr;
   cudaEvent_t done = nullptr;
   Arena d_src;                        // staged sources
+  Arena h_src;                        // page-locked bounce block for sources in ordinary host memory
+  cudaEvent_t src_copied = nullptr;   // the bounce block has left for the device
   Arena d_out;                        // batch written by the kernel when dst is host memory
   Arena d_desc[kDescSlots];           // DevSample tables
   Arena h_desc[kDescSlots];           // their pinned images
   cudaEvent_t desc_copied[kDescSlots] = {};
   cudaEvent_t k_begin[kDescSlots] = {};   // timing events around the kernel of each slot
   cudaEvent_t k_end[kDescSlots] = {};
+  cudaEvent_t in_begin[kDescSlots] = {};  // around the host-to-device stage (gather kernel or copies)
+  cudaEvent_t out_end[kDescSlots] = {};   // after the device-to-host copy of the batch (k_end is its start)
   bool k_pending[kDescSlots] = {};        // recorded, not yet added to the statistics
+  bool in_timed[kDescSlots] = {};
+  bool out_timed[kDescSlots] = {};
   int next_slot = 0;
   int32_t* d_status = nullptr;        // this lane's word of the context's status block
   int32_t* h_status = nullptr;        // pinned copy of the device status word
@@ -101,6 +107,7 @@ struct mlxd_ctx {
   std::map<mlxd::LutKey, float*> luts;
   std::atomic<uint64_t> batches{0}, samples{0}, launches{0}, h2d{0}, d2h{0}, reserved{0};
   std::atomic<uint64_t> kernel_ns{0}, timed_launches{0};
+  std::atomic<uint64_t> h2d_ns{0}, d2h_ns{0}, host_stage_ns{0};
   std::atomic<uint64_t> algo_src{0}, algo_dst{0};
   std::atomic<int> timing{0};
 };

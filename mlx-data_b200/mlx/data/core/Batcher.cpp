@@ -75,7 +75,8 @@ Batcher::Batcher(
     : ops_(std::move(ops)),
       pad_values_(std::move(pad_values)),
       batch_dims_(std::move(batch_dims)),
-      casts_(std::move(casts)) {}
+      casts_(std::move(casts)),
+      placement_(gpu::Runtime::get().placement()) {}
 
 Sample Batcher::run(const std::vector<Sample>& raw) const {
   if (raw.empty()) {
@@ -130,7 +131,7 @@ Sample Batcher::run(const std::vector<Sample>& raw) const {
         if (c.ikey != key) {
           continue;
         }
-        auto f32 = gpu::Runtime::get().batch(images, pad, &c.spec);
+        auto f32 = gpu::Runtime::get().batch(images, pad, &c.spec, placement_);
         if (c.okey.empty() || c.okey == key) {
           out[key] = f32;
           replaced = true;
@@ -139,7 +140,7 @@ Sample Batcher::run(const std::vector<Sample>& raw) const {
         }
       }
       if (!replaced) {
-        out[key] = gpu::Runtime::get().batch(images, pad, nullptr);
+        out[key] = gpu::Runtime::get().batch(images, pad, nullptr, placement_);
       }
       continue;
     }

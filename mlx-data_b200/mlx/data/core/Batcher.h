@@ -43,12 +43,14 @@ class Batcher {
   const std::unordered_map<std::string, double>& pad_values() const { return pad_values_; }
   const std::unordered_map<std::string, int>& batch_dims() const { return batch_dims_; }
   const std::vector<CastRequest>& casts() const { return casts_; }
+  const gpu::Placement& placement() const { return placement_; }
 
  private:
   std::vector<std::shared_ptr<op::ImageTransformOp>> ops_;
   std::unordered_map<std::string, double> pad_values_;
   std::unordered_map<std::string, int> batch_dims_;
   std::vector<CastRequest> casts_;
+  gpu::Placement placement_;   // the process-wide defaults at the time the node was built
 };
 
 } // namespace core

@@ -187,7 +187,8 @@ void LazyImage::describe(mlxd_sample_desc& d) const {
 
 std::shared_ptr<Array> LazyImage::materialise() const {
   std::vector<LazyImage> one{*this};
-  auto batched = Runtime::get().batch(one, 0.0, nullptr);
+  // an image between two ops lives in host memory, like every op result of the reference
+  auto batched = Runtime::get().batch(one, 0.0, nullptr, Placement());
   // drop the leading batch dimension; storage is shared
   return std::make_shared<Array>(
       batched->type(), std::vector<int64_t>{batched->shape(1), batched->shape(2), batched->shape(3)},
@@ -268,12 +269,19 @@ void Runtime::release_lane(int ln) {
 Runtime::~Runtime() {}
 
 void Runtime::set_device_output(bool on) {
-  device_output_ = on;
+  std::lock_guard<std::mutex> g(mu_);
+  defaults_.device_output = on;
 }
 
 void Runtime::set_stream(void* cuda_stream, bool enabled) {
-  ext_stream_ = cuda_stream;
-  use_ext_stream_ = enabled;
+  std::lock_guard<std::mutex> g(mu_);
+  defaults_.stream = cuda_stream;
+  defaults_.use_stream = enabled;
+}
+
+Placement Runtime::placement() const {
+  std::lock_guard<std::mutex> g(mu_);
+  return defaults_;
 }
 
 void* Runtime::pool_take(Pool& pool, size_t bytes, size_t& held) {
@@ -339,7 +347,8 @@ std::shared_ptr<Array> Runtime::device_array(ArrayType type, const std::vector<i
   return pooled_array(type, shape, true);
 }
 
-std::shared_ptr<Array> Runtime::batch(const std::vector<LazyImage>& images, double pad_value, const CastSpec* cast) {
+std::shared_ptr<Array> Runtime::batch(
+    const std::vector<LazyImage>& images, double pad_value, const CastSpec* cast, const Placement& where) {
   if (images.empty()) {
     throw std::runtime_error("Array: cannot batch an empty list of arrays");
   }
@@ -365,7 +374,7 @@ std::shared_ptr<Array> Runtime::batch(const std::vector<LazyImage>& images, doub
     throw std::runtime_error("batch: a batch cannot mix host and GPU-resident images");
   }
   const bool src_dev = on_device == n;
-  const bool dst_dev = device_output_;
+  const bool dst_dev = where.device_output;
   mlxd_batch_desc b;
   std::memset(&b, 0, sizeof(b));
   b.slot_h = to_i32(max_h, "height");
@@ -392,9 +401,9 @@ std::shared_ptr<Array> Runtime::batch(const std::vector<LazyImage>& images, doub
   auto out = dst_dev ? device_array(out_type, shape) : pinned_array(out_type, shape);
   b.dst = out->data();
   mlxd_ctx* c = ctx();
-  if (src_dev && dst_dev && use_ext_stream_) {
+  if (src_dev && dst_dev && where.use_stream) {
     // everything stays on the GPU: queue on the caller's stream and return
-    check(mlxd_fused_batch_on_stream(c, ext_stream_, descs.data(), n, &b));
+    check(mlxd_fused_batch_on_stream(c, where.stream, descs.data(), n, &b));
     return out;
   }
   // one lane per call in flight, whatever thread makes the call

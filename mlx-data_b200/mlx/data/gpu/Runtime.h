@@ -36,6 +36,16 @@ struct Window {
   void crop(int64_t cx, int64_t cy, int64_t cw, int64_t ch);
 };
 
+// Where a batch node leaves its results and on which stream it may queue work.
+// A node copies the process-wide defaults when it is built and keeps its copy:
+// placement is a property of a pipeline, later changes of the defaults do not
+// reach pipelines that already exist.
+struct Placement {
+  bool device_output = false;   // leave batches in GPU memory instead of page-locked host memory
+  void* stream = nullptr;       // caller-owned CUDA stream for all-GPU work
+  bool use_stream = false;
+};
+
 class LazyImage {
  public:
   // Checks that src looks like an image the way core::image::verify_image does.
@@ -104,7 +114,9 @@ class Runtime {
   // Where batch() and cast() leave their results: host (default, what
   // mlx-data does) or the GPU's memory, for consumers that train on that GPU.
   void set_device_output(bool on);
-  bool device_output() const { return device_output_; }
+  bool device_output() const { return placement().device_output; }
+  // The defaults a batch node built now would take.
+  Placement placement() const;
   // Launch on a caller-owned CUDA stream instead of the lanes.  Only used for
   // work whose sources and result are all in GPU memory; such calls return
   // without waiting and the result is ordered on that stream.
@@ -112,7 +124,8 @@ class Runtime {
 
   // One fused launch: every image's program, batch + pad, optional cast.
   // Result is [N, max_h, max_w, C] uint8, or float32 when cast is given.
-  std::shared_ptr<Array> batch(const std::vector<LazyImage>& images, double pad_value, const CastSpec* cast);
+  std::shared_ptr<Array> batch(
+      const std::vector<LazyImage>& images, double pad_value, const CastSpec* cast, const Placement& where);
 
   // Cast an existing uint8 array (any shape, last dimension = channels <= 4).
   std::shared_ptr<Array> cast(const std::shared_ptr<const Array>& arr, const CastSpec& spec);
@@ -130,11 +143,9 @@ class Runtime {
   bool pool_give(Pool& pool, void* p, size_t bytes);
   std::shared_ptr<Array> pooled_array(ArrayType type, const std::vector<int64_t>& shape, bool on_device);
   Pool device_pool_;
-  bool device_output_ = false;
-  void* ext_stream_ = nullptr;
-  bool use_ext_stream_ = false;
+  Placement defaults_;          // guarded by mu_
 
-  std::mutex mu_;
+  mutable std::mutex mu_;
   mlxd_ctx* ctx_ = nullptr;
   int n_lanes_ = 8;
   std::vector<int> free_lanes_;

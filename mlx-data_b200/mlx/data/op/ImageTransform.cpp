@@ -101,7 +101,7 @@ std::shared_ptr<Array> ImageTransformOp::apply_clip(
     all.push_back(first.with_source(frame(f)));
   }
   // every frame has the same result size: the "batch" is the clip, nothing is padded
-  return gpu::Runtime::get().batch(all, 0.0, nullptr);
+  return gpu::Runtime::get().batch(all, 0.0, nullptr, gpu::Placement());
 }
 
 // ------------------------------------------------------------ resize

@@ -565,14 +565,28 @@ PYBIND11_MODULE(_c, m) {
            "A numpy array in page-locked host memory: samples stored in such arrays are copied to the "
            "GPU asynchronously at full PCIe speed.");
   core.def("set_device_output", [](bool on) { gpu::Runtime::get().set_device_output(on); }, py::arg("on"),
-           "Leave batches in GPU memory (returned as DeviceArray) instead of copying them to the host.");
+           "Default for batch nodes built from now on: leave batches in GPU memory (returned as DeviceArray) "
+           "instead of copying them to the host.  A pipeline keeps the setting it was built with.");
   core.def("set_stream",
            [](uintptr_t stream, bool enabled) {
              gpu::Runtime::get().set_stream(reinterpret_cast<void*>(stream), enabled);
            },
            py::arg("cuda_stream"), py::arg("enabled") = true,
-           "Queue GPU-to-GPU work (GPU-resident samples and device output) on this CUDA stream handle "
-           "without waiting for it; pass enabled=False to go back to the internal lanes.");
+           "Default for batch nodes built from now on: queue GPU-to-GPU work (GPU-resident samples and device "
+           "output) on this CUDA stream handle without waiting for it; enabled=False goes back to the internal "
+           "lanes.  A pipeline keeps the setting it was built with.");
+  core.def("stream_status",
+           [](uintptr_t stream) {
+             int32_t word = 0;
+             const int rc = mlxd_stream_status(gpu::Runtime::get().ctx(), reinterpret_cast<void*>(stream), &word);
+             if (rc != MLXD_OK && rc != MLXD_ERR_DEVICE) {
+               gpu::Runtime::get().check(rc);
+             }
+             return word;
+           },
+           py::arg("cuda_stream"),
+           "Wait for the stream and return the self-check word of the kernels queued on it (0 = clean); "
+           "reading clears it.");
   core.def("set_timing",
            [](bool on) { gpu::Runtime::get().check(mlxd_ctx_set_timing(gpu::Runtime::get().ctx(), on ? 1 : 0)); },
            py::arg("on"), "Time every fused kernel with CUDA events; totals appear in stats().");
@@ -590,6 +604,9 @@ PYBIND11_MODULE(_c, m) {
     d["timed_launches"] = s.timed_launches;
     d["algo_src_bytes"] = s.algo_src_bytes;
     d["algo_dst_bytes"] = s.algo_dst_bytes;
+    d["h2d_ns"] = s.h2d_ns;
+    d["d2h_ns"] = s.d2h_ns;
+    d["host_stage_ns"] = s.host_stage_ns;
     return d;
   });
 }

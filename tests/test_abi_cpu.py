@@ -30,7 +30,7 @@ def test_struct_layouts_match_header(pkg):
     assert capi.SampleDesc.mx.offset == 48 and capi.SampleDesc.post_x.offset == 72
     assert capi.BatchDesc.pad_value.offset % 8 == 0
     assert ctypes.sizeof(capi.BatchDesc) == 104
-    assert ctypes.sizeof(capi.Stats) == 80
+    assert ctypes.sizeof(capi.Stats) == 104
 
 
 def test_calls_without_a_gpu_fail_loudly(pkg):
