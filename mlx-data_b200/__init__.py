@@ -14,7 +14,7 @@ fails, and without a CUDA device the first op raises.
 """
 from . import _capi  # noqa: F401
 from ._capi import Context, MlxdError, make_batch_desc, SAMPLE_DTYPE  # noqa: F401
-from ._c import Buffer, Stream, buffer_from_vector, core  # noqa: F401
+from ._c import Buffer, Stream, buffer_from_vector, stream_python_iterable, core  # noqa: F401
 
-__all__ = ["Buffer", "Stream", "buffer_from_vector", "core",
+__all__ = ["Buffer", "Stream", "buffer_from_vector", "stream_python_iterable", "core",
            "Context", "MlxdError", "make_batch_desc", "SAMPLE_DTYPE", "_capi"]

@@ -26,6 +26,19 @@ Stream Stream::batch(
   return Stream(std::make_shared<stream::Batch>(self_, batch_size, pad_values, batch_dims));
 }
 
+Stream Stream::dynamic_batch(
+    int64_t buffer_size, const std::string& key, int64_t min_data_size, int64_t max_data_size,
+    const std::unordered_map<std::string, double>& pad_values, const std::unordered_map<std::string, int>& batch_dims,
+    bool shuffle, bool drop_outliers, int64_t max_skipped_samples, int num_thread) const {
+  return Stream(std::make_shared<stream::DynamicBatch>(
+      self_, buffer_size, key, min_data_size, max_data_size, pad_values, batch_dims, shuffle, drop_outliers,
+      max_skipped_samples, num_thread));
+}
+
+Stream Stream::repeat(int64_t num_time) const {
+  return Stream(std::make_shared<stream::Repeat>(self_, num_time));
+}
+
 Stream Stream::partition(int64_t num_partitions, int64_t partition) const {
   return Stream(std::make_shared<stream::Partition>(self_, num_partitions, partition));
 }
@@ -104,6 +117,14 @@ Buffer Buffer::partition(int64_t num_partitions, int64_t partition) const {
 
 Buffer Buffer::partition_if(bool cond, int64_t num_partitions, int64_t partition) const {
   return cond ? this->partition(num_partitions, partition) : Buffer(self_);
+}
+
+Buffer Buffer::shuffle() const {
+  return Buffer(buffer::shuffled(self_));
+}
+
+Buffer Buffer::shuffle_if(bool cond) const {
+  return cond ? this->shuffle() : Buffer(self_);
 }
 
 Stream Buffer::to_stream() {

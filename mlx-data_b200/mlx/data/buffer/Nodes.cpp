@@ -3,6 +3,8 @@
 #include <algorithm>
 #include <stdexcept>
 
+#include "mlx/data/core/State.h"
+
 namespace mlx {
 namespace data {
 namespace buffer {
@@ -278,77 +280,121 @@ class RunShape {
 
 } // namespace
 
+// The grouping rule, stated over the (size-ordered) sequence of samples:
+//
+//   a run starts at the first sample not yet placed and grows one sample at a
+//   time; after every sample the padded size of the run is looked at and the
+//   run ends by one of four verdicts, else keeps growing.
+//     Emit      - both limits are given and the size lies between them;
+//                 also a lone sample over the upper limit when outliers are kept
+//     Drop      - a lone sample over the upper limit when outliers are dropped
+//     EmitShort - over the upper limit and no lower limit: the run without its
+//                 last sample is a batch; the last sample starts the next run
+//                 and is not looked at on its own there (so an oversized
+//                 sample arriving this way leaves as a batch of one when the
+//                 next sample comes, whatever drop_outliers says)
+//     LeaveOut  - over the upper limit with a lower limit (the run was too
+//                 small before this sample and is too large with it)
+//   A run still growing when the samples end is emitted if it respects the
+//   limits that are given and left out otherwise.
+//
+// This restates what mlx/data/buffer/DynamicBatch.cpp:101-204 computes (same
+// batches, same skipped samples, in the same order); the statement above is
+// the specification, the reference is where it was read from.
+namespace {
+enum class Verdict { Grow, Emit, Drop, EmitShort, LeaveOut };
+
+struct Limits {
+  int64_t lo, hi;  // <= 0: not given
+  bool drop_outliers;
+
+  bool above(int64_t size) const { return hi > 0 && size > hi; }
+  bool respects(int64_t size) const { return (lo <= 0 || size >= lo) && !above(size); }
+
+  Verdict after_adding(int64_t size, int64_t run_length, bool inherited_first) const {
+    if (run_length == 1 && inherited_first) {
+      return Verdict::Grow;
+    }
+    if (lo > 0 && hi > 0 && respects(size)) {
+      return Verdict::Emit;
+    }
+    if (!above(size)) {
+      return Verdict::Grow;
+    }
+    if (run_length == 1) {
+      return drop_outliers ? Verdict::Drop : Verdict::Emit;
+    }
+    return lo > 0 ? Verdict::LeaveOut : Verdict::EmitShort;
+  }
+};
+} // namespace
+
 DynamicGroups dynamic_groups(
     const std::vector<std::vector<int64_t>>& shapes, int64_t min_data_size, int64_t max_data_size,
     bool has_batch_dim, int batch_dim, bool drop_outliers) {
   const int64_t n = static_cast<int64_t>(shapes.size());
-  std::vector<int64_t> elements(n, 0);
+  std::vector<int64_t> by_size(n);
   for (int64_t i = 0; i < n; i++) {
-    if (!shapes[i].empty()) {
-      int64_t e = 1;
-      for (auto d : shapes[i]) {
-        e *= d;
-      }
-      elements[i] = e;
-    }
-  }
-  std::vector<int64_t> sorted(n);
-  for (int64_t i = 0; i < n; i++) {
-    sorted[i] = i;
+    by_size[i] = i;
   }
   if (max_data_size > 0) {
-    std::stable_sort(sorted.begin(), sorted.end(), [&](int64_t a, int64_t b) { return elements[a] < elements[b]; });
+    // an array without dimensions counts as empty here
+    std::vector<int64_t> volume(n, 0);
+    for (int64_t i = 0; i < n; i++) {
+      if (!shapes[i].empty()) {
+        volume[i] = 1;
+        for (auto d : shapes[i]) {
+          volume[i] *= d;
+        }
+      }
+    }
+    std::stable_sort(by_size.begin(), by_size.end(), [&](int64_t a, int64_t b) { return volume[a] < volume[b]; });
   }
 
+  const Limits limits{min_data_size, max_data_size, drop_outliers};
   DynamicGroups out;
   out.order.reserve(n);
-  RunShape run(has_batch_dim, batch_dim);
-  // the run ends at position `last` of the sorted order and holds `count` samples
-  auto accept = [&](int64_t last, int64_t count) {
-    out.batch_sizes.push_back(count);
-    out.order.insert(out.order.end(), sorted.begin() + (last + 1 - count), sorted.begin() + (last + 1));
-    run.clear();
+  auto emit = [&](int64_t first, int64_t past) {
+    out.batch_sizes.push_back(past - first);
+    out.order.insert(out.order.end(), by_size.begin() + first, by_size.begin() + past);
   };
-  auto skip = [&](int64_t last, int64_t count) {
-    out.skipped.insert(out.skipped.end(), sorted.begin() + (last + 1 - count), sorted.begin() + (last + 1));
-    run.clear();
+  auto leave_out = [&](int64_t first, int64_t past) {
+    out.skipped.insert(out.skipped.end(), by_size.begin() + first, by_size.begin() + past);
   };
-  const bool has_min = min_data_size > 0;
-  const bool has_max = max_data_size > 0;
-  for (int64_t i = 0; i < n; i++) {
-    run.add(shapes[sorted[i]]);
-    const int64_t size = run.elements();
-    if (has_min && size >= min_data_size && has_max && size <= max_data_size) {
-      accept(i, run.count());
-      continue;
+
+  int64_t first = 0;  // where the current run starts in by_size
+  bool inherited_first = false;  // the run's first sample is the one an EmitShort pushed out
+  while (first < n) {
+    RunShape run(has_batch_dim, batch_dim);
+    Verdict verdict = Verdict::Grow;
+    int64_t past = first;  // one past the run's last sample
+    while (past < n && verdict == Verdict::Grow) {
+      run.add(shapes[by_size[past++]]);
+      verdict = limits.after_adding(run.elements(), past - first, inherited_first);
     }
-    if (has_max && size > max_data_size) {
-      if (run.count() == 1) {
-        // a single sample over the limit: kept as a batch of one unless outliers are dropped
-        if (!drop_outliers) {
-          accept(i, 1);
+    inherited_first = verdict == Verdict::EmitShort;
+    switch (verdict) {
+      case Verdict::Grow:  // the samples ended first
+        if (limits.respects(run.elements())) {
+          emit(first, past);
         } else {
-          run.clear();
+          leave_out(first, past);
         }
-        continue;
-      }
-      if (has_min) {
-        // too small before this sample, too large with it: leave the run out
-        skip(i, run.count());
-      } else {
-        // close the run before this sample and start the next one with it
-        accept(i - 1, run.count() - 1);
-        run.add(shapes[sorted[i]]);
-      }
+        break;
+      case Verdict::Emit:
+        emit(first, past);
+        break;
+      case Verdict::Drop:
+        break;
+      case Verdict::EmitShort:
+        past -= 1;
+        emit(first, past);
+        break;
+      case Verdict::LeaveOut:
+        leave_out(first, past);
+        break;
     }
-  }
-  if (run.count() > 0) {
-    const int64_t size = run.elements();
-    if ((!has_min || size >= min_data_size) && (!has_max || size <= max_data_size)) {
-      accept(n - 1, run.count());
-    } else {
-      skip(n - 1, run.count());
-    }
+    first = past;
   }
   return out;
 }
@@ -356,7 +402,7 @@ DynamicGroups dynamic_groups(
 std::shared_ptr<Buffer> dynamic_batch(
     const std::shared_ptr<Buffer>& source, const std::shared_ptr<Buffer>& size_source, const std::string& key,
     int64_t min_data_size, int64_t max_data_size, const std::unordered_map<std::string, double>& pad_values,
-    const std::unordered_map<std::string, int>& batch_dims, bool drop_outliers) {
+    const std::unordered_map<std::string, int>& batch_dims, bool drop_outliers, std::vector<int64_t>* skipped) {
   const int64_t n = source->size();
   if (size_source && size_source->size() != n) {
     throw std::runtime_error("DynamicBatch: buffer and reference size buffer do not match in size");
@@ -375,6 +421,9 @@ std::shared_ptr<Buffer> dynamic_batch(
   const DynamicGroups g = dynamic_groups(
       shapes, min_data_size, max_data_size, dim != batch_dims.end(), dim != batch_dims.end() ? dim->second : 0,
       drop_outliers);
+  if (skipped) {
+    *skipped = g.skipped;
+  }
   // keep the image ops on top of the permutation, where Batch can fuse them
   std::vector<std::shared_ptr<op::ImageTransformOp>> ops;
   std::shared_ptr<Buffer> top = std::make_shared<Perm>(peel_image_ops(source, ops), g.order);
@@ -383,6 +432,15 @@ std::shared_ptr<Buffer> dynamic_batch(
     top = std::make_shared<Transform>(top, generic);
   }
   return std::make_shared<Batch>(top, g.batch_sizes, pad_values, batch_dims);
+}
+
+std::shared_ptr<Buffer> shuffled(const std::shared_ptr<Buffer>& source) {
+  std::vector<int64_t> order(source->size());
+  for (size_t i = 0; i < order.size(); i++) {
+    order[i] = static_cast<int64_t>(i);
+  }
+  std::shuffle(order.begin(), order.end(), core::get_state()->randomGenerator);
+  return std::make_shared<Perm>(source, order);
 }
 
 } // namespace buffer

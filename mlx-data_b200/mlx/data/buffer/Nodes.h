@@ -110,11 +110,17 @@ DynamicGroups dynamic_groups(
     bool has_batch_dim, int batch_dim, bool drop_outliers);
 
 // source.dynamic_batch(...): the shapes come from `size_source` (int64 arrays
-// under `key`) when given, else from the samples themselves.
+// under `key`) when given, else from the samples themselves.  `skipped`, when
+// given, receives the indices of the samples that ended up in no batch.
 std::shared_ptr<Buffer> dynamic_batch(
     const std::shared_ptr<Buffer>& source, const std::shared_ptr<Buffer>& size_source, const std::string& key,
     int64_t min_data_size, int64_t max_data_size, const std::unordered_map<std::string, double>& pad_values,
-    const std::unordered_map<std::string, int>& batch_dims, bool drop_outliers);
+    const std::unordered_map<std::string, int>& batch_dims, bool drop_outliers,
+    std::vector<int64_t>* skipped = nullptr);
+
+// The buffer in a random order drawn from the calling thread's core::State
+// (std::shuffle of the identity, as mlx/data/buffer/Shuffle.cpp:16-22 draws it).
+std::shared_ptr<Buffer> shuffled(const std::shared_ptr<Buffer>& source);
 
 // Split a chain "source -> Transform(image op) -> ... -> Transform(image op)"
 // into its non-image base and the list of image ops above it.

@@ -3,6 +3,8 @@
 #include <algorithm>
 #include <stdexcept>
 
+#include "mlx/data/buffer/Nodes.h"
+
 namespace mlx {
 namespace data {
 namespace stream {
@@ -252,6 +254,140 @@ Sample Partition::next() const {
 void Partition::reset() {
   std::lock_guard<std::mutex> g(mu_);
   source_->reset();
+}
+
+// ------------------------------------------------------------ Repeat
+Sample Repeat::next() const {
+  {
+    std::shared_lock<std::shared_mutex> pulling(mu_);
+    Sample s = source_->next();
+    if (!s.empty()) {
+      return s;
+    }
+  }
+  // The source looked dry.  Whoever gets the exclusive lock first restarts it;
+  // the others find samples again when their turn comes.
+  std::unique_lock<std::shared_mutex> restarting(mu_);
+  Sample s = source_->next();
+  if (!s.empty()) {
+    return s;
+  }
+  if (num_time_ > 0 && restarts_ >= num_time_) {
+    return s;  // all passes done
+  }
+  restarts_++;
+  source_->reset();
+  return source_->next();
+}
+
+void Repeat::reset() {
+  std::unique_lock<std::shared_mutex> restarting(mu_);
+  source_->reset();
+  restarts_ = 0;
+}
+
+// ------------------------------------------------------------ DynamicBatch
+DynamicBatch::DynamicBatch(
+    const std::shared_ptr<Stream>& source, int64_t buffer_size, const std::string& key, int64_t min_data_size,
+    int64_t max_data_size, const std::unordered_map<std::string, double>& pad_values,
+    const std::unordered_map<std::string, int>& batch_dims, bool shuffle, bool drop_outliers,
+    int64_t max_skipped_samples, int num_thread)
+    : source_(source),
+      buffer_size_(buffer_size),
+      key_(key),
+      min_data_size_(min_data_size),
+      max_data_size_(max_data_size),
+      pad_values_(pad_values),
+      batch_dims_(batch_dims),
+      shuffle_(shuffle),
+      drop_outliers_(drop_outliers),
+      max_skipped_samples_(max_skipped_samples),
+      pullers_(std::make_shared<core::ThreadPool>(std::max(num_thread, 1))),
+      planner_(std::make_shared<core::ThreadPool>(1)) {
+  if (buffer_size <= 0) {
+    throw std::runtime_error("DynamicBatch: buffer size must be positive");
+  }
+}
+
+DynamicBatch::~DynamicBatch() {
+  if (next_round_.valid()) {
+    next_round_.wait();
+  }
+  planner_.reset();  // joins; its task is the only user of pullers_ and left_out_
+  pullers_.reset();
+}
+
+std::shared_ptr<buffer::Buffer> DynamicBatch::make_round() const {
+  std::vector<std::future<Sample>> pulls;
+  pulls.reserve(buffer_size_);
+  for (int64_t i = 0; i < buffer_size_; i++) {
+    pulls.push_back(pullers_->enqueue([s = source_] { return s->next(); }));
+  }
+  std::vector<Sample> samples;
+  samples.reserve(buffer_size_ + left_out_.size());
+  std::exception_ptr failed;
+  for (auto& f : pulls) {
+    try {
+      Sample s = f.get();
+      if (!s.empty()) {
+        samples.push_back(std::move(s));
+      }
+    } catch (...) {
+      failed = failed ? failed : std::current_exception();  // still collect the rest: they hold the source
+    }
+  }
+  if (failed) {
+    std::rethrow_exception(failed);
+  }
+  // new samples first, then the ones carried over
+  samples.insert(samples.end(), left_out_.begin(), left_out_.end());
+  left_out_.clear();
+
+  auto pulled = std::make_shared<buffer::FromVector>(samples);
+  std::vector<int64_t> skipped;
+  std::shared_ptr<buffer::Buffer> batches = buffer::dynamic_batch(
+      pulled, nullptr, key_, min_data_size_, max_data_size_, pad_values_, batch_dims_, drop_outliers_, &skipped);
+  if (max_skipped_samples_ > 0 && static_cast<int64_t>(skipped.size()) > max_skipped_samples_) {
+    skipped.resize(max_skipped_samples_);
+  }
+  for (auto idx : skipped) {
+    left_out_.push_back(samples[idx]);
+  }
+  return shuffle_ ? buffer::shuffled(batches) : batches;
+}
+
+std::future<std::shared_ptr<buffer::Buffer>> DynamicBatch::start_round() const {
+  return planner_->enqueue([this] { return make_round(); });
+}
+
+Sample DynamicBatch::next() const {
+  std::lock_guard<std::mutex> g(mu_);
+  if (!round_) {
+    round_ = start_round().get();
+    next_round_ = start_round();
+  } else if (round_->size() > 0 && cursor_ >= round_->size()) {
+    cursor_ = 0;
+    round_ = next_round_.get();
+    next_round_ = start_round();
+  }
+  if (round_->size() == 0) {
+    return Sample();  // a round without a batch ends the stream (until reset)
+  }
+  return round_->get(cursor_++);
+}
+
+void DynamicBatch::reset() {
+  std::lock_guard<std::mutex> g(mu_);
+  if (next_round_.valid()) {
+    try {
+      next_round_.get();  // its samples are discarded with it
+    } catch (...) {
+    }
+  }
+  round_.reset();
+  cursor_ = 0;
+  source_->reset();
+  // samples left out so far stay in line for the next round, as in the reference
 }
 
 } // namespace stream

@@ -1,12 +1,14 @@
 // Stream nodes of the transform-and-batch path: FromBuffer, Transform, Batch,
-// Prefetch, OrderedPrefetch, Partition (roles of the same-named files under
-// mlx/data/stream/).
+// DynamicBatch, Prefetch, OrderedPrefetch, Partition, Repeat (roles of the
+// same-named files under mlx/data/stream/).
 #pragma once
 
 #include <deque>
 #include <future>
 #include <memory>
 #include <mutex>
+#include <shared_mutex>
+#include <string>
 #include <unordered_map>
 #include <vector>
 
@@ -115,6 +117,65 @@ class Partition : public Stream {
  private:
   std::shared_ptr<Stream> source_;
   int64_t num_partitions_, partition_;
+  mutable std::mutex mu_;
+};
+
+// Start the source over when it runs dry: num_time more passes after the
+// first, without end when num_time <= 0 (mlx/data/stream/Repeat.cpp:14-48).
+class Repeat : public Stream {
+ public:
+  Repeat(const std::shared_ptr<Stream>& source, int64_t num_time) : source_(source), num_time_(num_time) {}
+  Sample next() const override;
+  void reset() override;
+
+ private:
+  std::shared_ptr<Stream> source_;
+  int64_t num_time_;
+  mutable int64_t restarts_ = 0;
+  mutable std::shared_mutex mu_;  // shared: pulling; exclusive: restarting the source
+};
+
+// Size-aware batching over a stream (mlx/data/stream/DynamicBatch.cpp:35-70 on
+// top of stream/Buffered.cpp:22-98): pull `buffer_size` samples, append the
+// samples the previous round left out, group them with buffer::dynamic_batch,
+// optionally shuffle the batches, hand them out one by one; then pull again.
+// Samples a round leaves out (at most max_skipped_samples of them when that is
+// positive) get another chance in the next round.  The stream ends with the
+// first round that yields no batch.  The next round is prepared on a worker
+// thread while the current one is handed out; its samples are pulled by
+// num_thread workers.  Samples are taken as the source delivers them - ops
+// above the source have run by then - so the sizes that drive the grouping
+// are the sizes that get batched; padding and stacking of image keys still
+// run as one GPU launch per batch.
+class DynamicBatch : public Stream {
+ public:
+  DynamicBatch(
+      const std::shared_ptr<Stream>& source, int64_t buffer_size, const std::string& key, int64_t min_data_size,
+      int64_t max_data_size, const std::unordered_map<std::string, double>& pad_values,
+      const std::unordered_map<std::string, int>& batch_dims, bool shuffle, bool drop_outliers,
+      int64_t max_skipped_samples, int num_thread);
+  ~DynamicBatch();
+  Sample next() const override;
+  void reset() override;
+
+ private:
+  std::shared_ptr<buffer::Buffer> make_round() const;
+  std::future<std::shared_ptr<buffer::Buffer>> start_round() const;
+
+  std::shared_ptr<Stream> source_;
+  int64_t buffer_size_;
+  std::string key_;
+  int64_t min_data_size_, max_data_size_;
+  std::unordered_map<std::string, double> pad_values_;
+  std::unordered_map<std::string, int> batch_dims_;
+  bool shuffle_, drop_outliers_;
+  int64_t max_skipped_samples_;
+  std::shared_ptr<core::ThreadPool> pullers_;               // num_thread workers calling the source
+  std::shared_ptr<core::ThreadPool> planner_;               // one worker building the next round
+  mutable std::vector<Sample> left_out_;                    // only touched by the planner thread's task
+  mutable std::shared_ptr<buffer::Buffer> round_;
+  mutable std::future<std::shared_ptr<buffer::Buffer>> next_round_;
+  mutable int64_t cursor_ = 0;
   mutable std::mutex mu_;
 };
 

@@ -390,6 +390,46 @@ struct BufferCursor {
   int64_t at = 0;
 };
 
+// A stream over a python iterable.  It is given the function that makes the
+// iterable, not the iterable, so that reset() can start over.  Python objects
+// are only touched with the interpreter lock held, which also serialises
+// concurrent next() calls.
+class PyIterableStream : public stream::Stream {
+ public:
+  explicit PyIterableStream(py::function factory) : factory_(new py::function(std::move(factory))) {}
+  ~PyIterableStream() override {
+    py::gil_scoped_acquire gil;
+    cursor_.reset();
+    factory_.reset();
+  }
+
+  Sample next() const override {
+    py::gil_scoped_acquire gil;
+    if (!cursor_) {
+      cursor_.reset(new py::iterator(py::iter((*factory_)())));
+    }
+    if (*cursor_ == py::iterator::sentinel()) {
+      return Sample();
+    }
+    py::handle item = **cursor_;
+    if (!py::isinstance<py::dict>(item)) {
+      throw std::invalid_argument("[stream_python_iterable] the iterable must yield dicts of arrays");
+    }
+    Sample s = to_sample(py::reinterpret_borrow<py::dict>(item));
+    ++(*cursor_);
+    return s;
+  }
+
+  void reset() override {
+    py::gil_scoped_acquire gil;
+    cursor_.reset();
+  }
+
+ private:
+  std::unique_ptr<py::function> factory_;
+  mutable std::unique_ptr<py::iterator> cursor_;
+};
+
 } // namespace
 
 PYBIND11_MODULE(_c, m) {
@@ -498,6 +538,8 @@ PYBIND11_MODULE(_c, m) {
       .def("partition", &Buffer::partition, nogil(), py::arg("num_partitions"), py::arg("partition"))
       .def("partition_if", &Buffer::partition_if, nogil(), py::arg("cond"), py::arg("num_partitions"),
            py::arg("partition"))
+      .def("shuffle", &Buffer::shuffle, nogil(), "The buffer in a random order (drawn once, here).")
+      .def("shuffle_if", &Buffer::shuffle_if, nogil(), py::arg("cond"))
       .def("to_stream", &Buffer::to_stream, nogil());
   bind_ops<Buffer>(buffer);
 
@@ -528,6 +570,16 @@ PYBIND11_MODULE(_c, m) {
       .def("__repr__", [](const Stream&) { return "Stream()"; })
       .def("reset", &Stream::reset, nogil())
       .def("batch", &Stream::batch, nogil(), py::arg("batch_size"), py::arg("pad") = MapD(), py::arg("dim") = MapI())
+      .def("dynamic_batch", &Stream::dynamic_batch, nogil(), py::arg("buffer_size"), py::arg("key"), py::kw_only(),
+           py::arg("min_data_size") = -1, py::arg("max_data_size") = -1, py::arg("pad") = MapD(),
+           py::arg("dim") = MapI(), py::arg("shuffle") = false, py::arg("drop_outliers") = false,
+           py::arg("max_skipped_samples") = 1000, py::arg("num_threads") = 1,
+           "Batches of about the same number of elements of the array at ``key``: ``buffer_size`` samples are "
+           "pulled at a time, ordered by size and cut into batches holding between ``min_data_size`` and "
+           "``max_data_size`` elements after padding; samples that fit nowhere (at most "
+           "``max_skipped_samples``) join the next pull.")
+      .def("repeat", &Stream::repeat, nogil(), py::arg("num_time"),
+           "Start the stream over ``num_time`` times before it ends; without end when ``num_time`` <= 0.")
       .def("partition", &Stream::partition, nogil(), py::arg("num_partitions"), py::arg("partition"))
       .def("partition_if", &Stream::partition_if, nogil(), py::arg("cond"), py::arg("num_partitions"),
            py::arg("partition"))
@@ -548,6 +600,13 @@ PYBIND11_MODULE(_c, m) {
           return buffer_from_vector(std::move(samples));
         },
         py::arg("data"), "Make a buffer from a list of dicts of arrays (numpy arrays are not copied).");
+
+  m.def("stream_python_iterable",
+        [](py::function iterable_factory) {
+          return Stream(std::make_shared<PyIterableStream>(std::move(iterable_factory)));
+        },
+        py::arg("iterable_factory"),
+        "A stream over the dicts of arrays that ``iterable_factory()`` yields; reset() calls the factory again.");
 
   py::module core = m.def_submodule("core", "Process-wide state");
   core.def("set_state", &core::set_state, py::arg("seed") = 1234,
