@@ -58,6 +58,14 @@ enum mlxd_mem { MLXD_MEM_HOST = 0, MLXD_MEM_DEVICE = 1 };
  * With geom == NONE the geometric output is the pre window itself and
  * geom_w, geom_h must equal pre_w, pre_h.  Random parameters (crop rectangles,
  * flip decisions) are drawn by the caller on the host.
+ *
+ * Resize with 4 channels: the reference passes the channel count to its resize
+ * library as the pixel layout (ImageTransform.cpp:49-58), and layout 4 is
+ * RGBA, whose colour channels are weighted by alpha while filtering.  The
+ * kernels behind this struct filter every channel independently, also for
+ * C == 4, so a 4-channel resize differs from the reference wherever alpha
+ * varies.  The pipeline layer above this ABI refuses such resizes unless the
+ * caller opted in; at this level the caller is expected to know.
  */
 typedef struct mlxd_sample_desc {
   const uint8_t* src; /* [src_h, src_w, C] */
@@ -218,7 +226,8 @@ MLXD_API int mlxd_stream_status(mlxd_ctx* ctx, void* cuda_stream, int32_t* statu
 /* One entry per named op, host buffers in and out, synchronous; for chains
  * that cannot be fused (a host callback between two ops).  Each runs the same
  * kernel with a one-stage program. */
-/* core::image::resize, mlx/data/core/image/ImageTransform.cpp:41-62 */
+/* core::image::resize, mlx/data/core/image/ImageTransform.cpp:41-62
+ * (c == 4: channels filtered independently, see mlxd_sample_desc) */
 MLXD_API int mlxd_image_resize(
     mlxd_ctx* ctx, const uint8_t* src, int h, int w, int c, uint8_t* dst, int dh, int dw);
 /* core::image::crop, mlx/data/core/image/ImageTransform.cpp:64-73 */

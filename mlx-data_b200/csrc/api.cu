@@ -263,6 +263,7 @@ int mlxd_fused_batch_on_stream(
   PassNeed need;
   mlxd_batch_desc b = *batch;
   Lane& ring = *ctx->lanes[ctx->n_user_lanes + 1];
+  LutUse table_in_use(ctx);
   LaunchParams p;
   int rc = prepare_launch(ctx, &b, n, p);
   if (rc != MLXD_OK) {

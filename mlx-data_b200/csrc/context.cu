@@ -338,6 +338,27 @@ void compute_cast_table(const mlxd_batch_desc* b, int c_out, float* table) {
   }
 }
 
+LutUse::LutUse(mlxd_ctx* ctx) {
+  bool full;
+  {
+    std::lock_guard<std::mutex> g(ctx->lut_mu);
+    full = ctx->luts.size() >= kMaxCastTables;
+  }
+  if (full) {
+    std::unique_lock<std::shared_mutex> alone(ctx->lut_users);
+    std::lock_guard<std::mutex> g(ctx->lut_mu);
+    if (ctx->luts.size() >= kMaxCastTables) {
+      DeviceGuard on_device(ctx->device);
+      cudaDeviceSynchronize();
+      for (auto& kv : ctx->luts) {
+        cudaFree(kv.second);
+      }
+      ctx->luts.clear();
+    }
+  }
+  hold_ = std::shared_lock<std::shared_mutex>(ctx->lut_users);
+}
+
 int get_lut(mlxd_ctx* ctx, const mlxd_batch_desc* b, int c_out, const float** lut) {
   LutKey key;
   std::memset(&key, 0, sizeof(key));
@@ -421,6 +442,7 @@ int enqueue_on_lane(
     return fail(MLXD_ERR_INVALID, "null batch destination");
   }
   MLXD_ON_DEVICE(ctx->device);
+  LutUse table_in_use(ctx);
   LaunchParams p;
   int rc = prepare_launch(ctx, batch, n, p);
   if (rc != MLXD_OK) {

@@ -7,6 +7,7 @@
 #include <atomic>
 #include <map>
 #include <mutex>
+#include <shared_mutex>
 #include <string>
 #include <vector>
 
@@ -104,7 +105,8 @@ struct mlxd_ctx {
   int n_user_lanes = 0;
   int32_t* d_status = nullptr;        // one self-check word per lane, 64 bytes apart
   std::mutex lut_mu;
-  std::map<mlxd::LutKey, float*> luts;
+  std::map<mlxd::LutKey, float*> luts;   // at most mlxd::kMaxCastTables entries, see LutUse
+  std::shared_mutex lut_users;           // shared: a launch being prepared holds a table pointer; exclusive: emptying the cache
   std::atomic<uint64_t> batches{0}, samples{0}, launches{0}, h2d{0}, d2h{0}, reserved{0};
   std::atomic<uint64_t> kernel_ns{0}, timed_launches{0};
   std::atomic<uint64_t> h2d_ns{0}, d2h_ns{0}, host_stage_ns{0};
@@ -154,6 +156,21 @@ int prepare_launch(mlxd_ctx* ctx, const mlxd_batch_desc* b, int n, LaunchParams&
 
 // Device cast table for a batch descriptor (cached per context).
 int get_lut(mlxd_ctx* ctx, const mlxd_batch_desc* b, int c_out, const float** lut);
+
+// The cache of cast tables is bounded: a caller that changes mean/std on every
+// call would otherwise grow it for ever.  Every entry point that prepares a
+// launch holds a LutUse from before prepare_launch() until its kernel is
+// queued.  Constructing one first empties a full cache - with the exclusive
+// lock, so no other thread sits between "has a table pointer" and "kernel
+// queued", and after the device has drained, so no queued kernel reads a
+// freed table.
+constexpr size_t kMaxCastTables = 256;   // 4 KB each at most
+class LutUse {
+ public:
+  explicit LutUse(mlxd_ctx* ctx);
+ private:
+  std::shared_lock<std::shared_mutex> hold_;
+};
 
 // Part of a sample's source that its chain can read: rows [r0, r1), columns
 // [c0, c1); `margin` widens a filter footprint by that many source samples.

@@ -1,5 +1,7 @@
 #include "mlx/data/gpu/Runtime.h"
 
+#include <atomic>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
@@ -109,6 +111,11 @@ bool LazyImage::resize(int64_t dw, int64_t dh) {
   }
   if (src_->type() != UInt8) {
     throw std::invalid_argument("image must be of type UInt8");
+  }
+  if (channels_ == 4 && !Runtime::rgba_resize_independent()) {
+    throw std::runtime_error(
+        "image resize: 4-channel images are filtered channel by channel here, while mlx-data weights colour by "
+        "alpha (RGBA layout of its resize library); call core.set_rgba_resize_independent(True) to accept that");
   }
   if (dh <= 0 || dw <= 0) {
     throw std::runtime_error("image: cannot create image with 0 or negative dimension");
@@ -267,6 +274,18 @@ void Runtime::release_lane(int ln) {
 }
 
 Runtime::~Runtime() {}
+
+namespace {
+std::atomic<bool> g_rgba_independent{false};
+}
+
+void Runtime::set_rgba_resize_independent(bool accept) {
+  g_rgba_independent.store(accept);
+}
+
+bool Runtime::rgba_resize_independent() {
+  return g_rgba_independent.load();
+}
 
 void Runtime::set_device_output(bool on) {
   std::lock_guard<std::mutex> g(mu_);

@@ -117,6 +117,14 @@ class Runtime {
   bool device_output() const { return placement().device_output; }
   // The defaults a batch node built now would take.
   Placement placement() const;
+  // Resizing a 4-channel image.  mlx-data hands such images to its resize
+  // library as RGBA, which weights the colour channels by alpha while it
+  // filters; the kernels here filter the four channels independently of one
+  // another, so the results differ wherever alpha varies.  The resize ops
+  // therefore refuse 4-channel images unless the caller has accepted the
+  // independent filtering here.
+  static void set_rgba_resize_independent(bool accept);
+  static bool rgba_resize_independent();
   // Launch on a caller-owned CUDA stream instead of the lanes.  Only used for
   // work whose sources and result are all in GPU memory; such calls return
   // without waiting and the result is ordered on that stream.

@@ -623,6 +623,10 @@ PYBIND11_MODULE(_c, m) {
            py::arg("shape"), py::arg("dtype") = "uint8",
            "A numpy array in page-locked host memory: samples stored in such arrays are copied to the "
            "GPU asynchronously at full PCIe speed.");
+  core.def("set_rgba_resize_independent", &gpu::Runtime::set_rgba_resize_independent, py::arg("accept"),
+           "Resizing 4-channel images: mlx-data weights colour by alpha while filtering, this library filters the "
+           "four channels independently, so results differ where alpha varies.  The resize ops refuse 4-channel "
+           "images until this is called with True.");
   core.def("set_device_output", [](bool on) { gpu::Runtime::get().set_device_output(on); }, py::arg("on"),
            "Default for batch nodes built from now on: leave batches in GPU memory (returned as DeviceArray) "
            "instead of copying them to the host.  A pipeline keeps the setting it was built with.");

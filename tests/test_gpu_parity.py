@@ -74,6 +74,9 @@ def test_channel_reduction(ctx, oracle, preset):
     ((1080, 1920, 3), (512, 910)), ((600, 800, 3), (60, 80)), ((1024, 64, 3), (320, 20)),
     ((900, 1300, 3), (40, 33)), ((100, 100, 3), (100, 37)), ((100, 100, 2), (51, 100))])
 def test_resize(ctx, oracle, shape, dst):
+    # The 4-channel case checks kernel against restatement only: both filter the
+    # four channels independently, while the reference's resize library treats
+    # 4 channels as RGBA and weights colour by alpha.  It is not a parity case.
     img = _rand(shape, 6)
     dh, dw = dst
     got = ctx.image_resize(img, dw, dh)
@@ -108,6 +111,22 @@ def test_cast(ctx, c):
     assert np.array_equal(got, (x.astype("float32") / 255 - mean) / std)
     big = _rand((3 * 4096 + 5, 1, c), 12)
     assert np.array_equal(ctx.cast_scale_normalise(big), big.astype("float32") / 255)
+
+
+def test_cast_with_more_parameter_sets_than_the_table_cache_holds(pkg):
+    """Every distinct (divisor, mean, std) gets a device table that the context
+    keeps; the cache is bounded (256 tables), emptied when full.  Results stay
+    exact across the emptying, also for parameter sets seen before it."""
+    own = pkg.Context(device=0, n_lanes=1)
+    try:
+        x = _rand((2, 9, 13, 3), 13)
+        std = np.array([0.229, 0.224, 0.225], np.float32)
+        for i in list(range(300)) + [0, 1, 299]:
+            mean = np.array([0.1 + i / 1000.0, 0.456, 0.406], np.float32)
+            got = own.cast_scale_normalise(x, 255.0, mean, std)
+            assert np.array_equal(got, (x.astype("float32") / 255 - mean) / std), i
+    finally:
+        own.close()
 
 
 # ---------------------------------------------------------------- fused chains

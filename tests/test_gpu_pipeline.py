@@ -136,6 +136,28 @@ def test_error_behaviour_matches(pkg):
         b[3]
 
 
+def test_four_channel_resize_is_refused_until_accepted(pkg, oracle):
+    """mlx-data weights colour by alpha when it resizes a 4-channel image; the
+    kernels filter the four channels independently.  The pipeline says so
+    instead of returning different pixels, and runs once the caller accepts."""
+    rng = np.random.default_rng(2)
+    img = rng.integers(0, 256, (40, 52, 4), dtype=np.uint8)
+    b = pkg.buffer_from_vector([{"image": img}])
+    with pytest.raises(RuntimeError, match="weights colour by alpha"):
+        b.image_resize("image", 20, 16)[0]
+    with pytest.raises(RuntimeError, match="weights colour by alpha"):
+        b.image_resize_smallest_side("image", 20).batch(1)[0]
+    # the other ops do not care about the channel count
+    assert np.array_equal(np.asarray(b.image_center_crop("image", 8, 8)[0]["image"]), img[16:24, 22:30])
+    pkg.core.set_rgba_resize_independent(True)
+    try:
+        got = np.asarray(b.image_resize("image", 20, 16)[0]["image"])
+        want = oracle.resize(img, 20, 16)      # the restatement, not the reference: independent channels too
+        assert got.shape == want.shape and np.abs(got.astype(int) - want.astype(int)).max() <= 1
+    finally:
+        pkg.core.set_rgba_resize_independent(False)
+
+
 CLIP_CHAINS = {
     "resize_crop_flip": [("image_resize_smallest_side", dict(key="image", size=48)),
                          ("image_random_crop", dict(key="image", w=40, h=36)),
