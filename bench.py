@@ -351,6 +351,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg")
     ap.add_argument("--quick-e2e", action="store_true", help="end-to-end leg without the device-output and pageable runs")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of one batch with the CPU oracle")
+    ap.add_argument("--host-affinity", default="auto", choices=["auto", "on", "off"],
+                    help="keep each rank's host threads on its GPU's NUMA node (auto: when more than one rank runs)")
     ap.add_argument("--repeats", type=int, default=0, help="times the K steps are repeated inside the timed region (0: about one second)")
     args = ap.parse_args()
     wl = load_workloads()
@@ -372,6 +374,11 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dx = load_package()
     dx.core.set_device(local)
+    numa = None
+    if args.host_affinity == "on" or (args.host_affinity == "auto" and world > 1):
+        # before any worker thread or page-locked block exists
+        node, cpus = dx.core.bind_host_threads_to_device_node()
+        numa = {"node": node, "cpus": cpus}
 
     batch = args.batch or cfg["full"]["batch"]
     K, W = args.steps, max(args.warmup, 3)
@@ -527,10 +534,12 @@ def main():
 
         e2e = run_host_leg(host_pool, Ke, False)
         e2e["host_memory"] = "page-locked (core.pinned_empty)"
+        e2e["host_cpus"] = len(os.sched_getaffinity(0))
+        e2e["numa"] = numa
         if world > 1:
             # every rank's breakdown, for the scaling picture
             gathered = [None] * world
-            dist.all_gather_object(gathered, e2e["breakdown"])
+            dist.all_gather_object(gathered, dict(e2e["breakdown"], numa=numa, host_cpus=e2e["host_cpus"]))
             e2e["breakdown_all_ranks"] = gathered
         if not args.quick_e2e:
             # batches left in HBM: what a trainer on the same GPU consumes

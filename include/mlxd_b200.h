@@ -143,6 +143,12 @@ MLXD_API const char* mlxd_last_error(void);
 MLXD_API void* mlxd_pinned_alloc(size_t bytes);
 MLXD_API void mlxd_pinned_free(void* p);
 
+/* PCI address of a CUDA device as "dddd:bb:dd.f" (NUL-terminated, len >= 16):
+ * the name of its directory under /sys/bus/pci/devices, where a host finds the
+ * NUMA node its loader threads and page-locked pools belong on.  (No
+ * counterpart in the reference.) */
+MLXD_API int mlxd_device_pci_bus_id(int device, char* out, size_t len);
+
 /* Device memory on the context's GPU, for sources and batches that stay in
  * HBM (no counterpart in the reference, which is host-only).  NULL on failure. */
 MLXD_API void* mlxd_device_alloc(mlxd_ctx* ctx, size_t bytes);

@@ -78,7 +78,7 @@ EXPORTS = [
     "mlxd_image_crop", "mlxd_image_hflip", "mlxd_image_affine", "mlxd_image_channel_reduction",
     "mlxd_batch_pad", "mlxd_cast_scale_normalise", "mlxd_stats_get",
     "mlxd_device_alloc", "mlxd_device_free", "mlxd_ctx_set_timing", "mlxd_fused_batch_noalloc",
-    "mlxd_noalloc_status", "mlxd_stream_status",
+    "mlxd_noalloc_status", "mlxd_stream_status", "mlxd_device_pci_bus_id",
 ]
 NOALLOC_MAX_SAMPLES = 1024
 
@@ -131,6 +131,7 @@ def load():
     lib.mlxd_fused_batch_noalloc.argtypes = [i32, vp, vp, i32, ctypes.POINTER(BatchDesc)]
     lib.mlxd_noalloc_status.argtypes = [i32, vp, ctypes.POINTER(ctypes.c_int32)]
     lib.mlxd_stream_status.argtypes = [vp, vp, ctypes.POINTER(ctypes.c_int32)]
+    lib.mlxd_device_pci_bus_id.argtypes = [i32, ctypes.c_char_p, ctypes.c_size_t]
     _lib = lib
     return lib
 
@@ -172,6 +173,15 @@ def fused_batch_noalloc(device, stream, descs, batch):
                                       ctypes.byref(batch))
     if rc != OK:
         raise MlxdError(rc, lib.mlxd_last_error().decode())
+
+
+def device_pci_bus_id(device):
+    """"dddd:bb:dd.f" of a CUDA device (its directory name under /sys/bus/pci/devices)."""
+    buf = ctypes.create_string_buffer(32)
+    rc = load().mlxd_device_pci_bus_id(device, buf, 32)
+    if rc != OK:
+        raise MlxdError(rc, load().mlxd_last_error().decode())
+    return buf.value.decode()
 
 
 def noalloc_status(device, stream):

@@ -167,6 +167,14 @@ void mlxd_ctx_destroy(mlxd_ctx* ctx) {
   delete ctx;
 }
 
+int mlxd_device_pci_bus_id(int device, char* out, size_t len) {
+  if (!out || len < 16) {
+    return fail(MLXD_ERR_INVALID, "mlxd_device_pci_bus_id: buffer of at least 16 bytes expected");
+  }
+  MLXD_CUDA(cudaDeviceGetPCIBusId(out, (int)len, device));
+  return MLXD_OK;
+}
+
 const char* mlxd_last_error(void) {
   g_last = error_text();
   return g_last.c_str();

@@ -60,17 +60,17 @@ int64_t Transform::size() const {
 }
 
 std::shared_ptr<Buffer> peel_image_ops(
-    const std::shared_ptr<Buffer>& top, std::vector<std::shared_ptr<op::ImageTransformOp>>& ops) {
+    const std::shared_ptr<Buffer>& top, std::vector<std::shared_ptr<op::FusableOp>>& ops) {
   std::shared_ptr<Buffer> cur = top;
-  std::vector<std::shared_ptr<op::ImageTransformOp>> rev;
+  std::vector<std::shared_ptr<op::FusableOp>> rev;
   for (;;) {
     auto t = std::dynamic_pointer_cast<Transform>(cur);
     if (!t) {
       break;
     }
-    std::vector<std::shared_ptr<op::ImageTransformOp>> mine;
+    std::vector<std::shared_ptr<op::FusableOp>> mine;
     for (auto& o : t->ops()) {
-      auto io = std::dynamic_pointer_cast<op::ImageTransformOp>(o);
+      auto io = std::dynamic_pointer_cast<op::FusableOp>(o);
       if (!io) {
         mine.clear();
         break;
@@ -92,7 +92,7 @@ void Batch::absorb(
     const std::shared_ptr<Buffer>& source,
     const std::unordered_map<std::string, double>& pad_values,
     const std::unordered_map<std::string, int>& batch_dims) {
-  std::vector<std::shared_ptr<op::ImageTransformOp>> ops;
+  std::vector<std::shared_ptr<op::FusableOp>> ops;
   base_ = peel_image_ops(source, ops);
   batcher_ = std::make_shared<core::Batcher>(ops, pad_values, batch_dims);
 }
@@ -425,7 +425,7 @@ std::shared_ptr<Buffer> dynamic_batch(
     *skipped = g.skipped;
   }
   // keep the image ops on top of the permutation, where Batch can fuse them
-  std::vector<std::shared_ptr<op::ImageTransformOp>> ops;
+  std::vector<std::shared_ptr<op::FusableOp>> ops;
   std::shared_ptr<Buffer> top = std::make_shared<Perm>(peel_image_ops(source, ops), g.order);
   if (!ops.empty()) {
     std::vector<std::shared_ptr<op::Op>> generic(ops.begin(), ops.end());

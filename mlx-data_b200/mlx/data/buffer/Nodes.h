@@ -125,7 +125,7 @@ std::shared_ptr<Buffer> shuffled(const std::shared_ptr<Buffer>& source);
 // Split a chain "source -> Transform(image op) -> ... -> Transform(image op)"
 // into its non-image base and the list of image ops above it.
 std::shared_ptr<Buffer> peel_image_ops(
-    const std::shared_ptr<Buffer>& top, std::vector<std::shared_ptr<op::ImageTransformOp>>& ops);
+    const std::shared_ptr<Buffer>& top, std::vector<std::shared_ptr<op::FusableOp>>& ops);
 
 } // namespace buffer
 } // namespace data

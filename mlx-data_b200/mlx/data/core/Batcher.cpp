@@ -22,7 +22,17 @@ bool gpu_image(const std::shared_ptr<Array>& a) {
   return a && a->type() == UInt8 && a->ndim() == 3 && a->shape(2) >= 1 && a->shape(2) <= 4 && a->size() > 0;
 }
 
-void run_op(LazySample& s, const op::ImageTransformOp& op) {
+std::shared_ptr<Array> lazy_pixels(const Entry& e) {
+  if (e.array) {
+    return e.array;
+  }
+  if (e.lazy->untouched()) {
+    return std::make_shared<Array>(e.lazy->source());
+  }
+  return e.lazy->materialise();
+}
+
+void run_op(LazySample& s, const op::FusableOp& op) {
   auto it = s.find(op.input_key());
   if (it == s.end()) {
     throw std::runtime_error("key <" + op.input_key() + "> expected");
@@ -30,7 +40,7 @@ void run_op(LazySample& s, const op::ImageTransformOp& op) {
   Entry in = it->second;
   Entry out;
   if (!in.lazy && !gpu_image(in.array)) {
-    // videos, non-uint8 arrays, malformed images: the op decides (and throws)
+    // videos, non-uint8 arrays, token arrays, malformed images: the op decides (and throws)
     out.array = op.apply_key(in.array);
   } else {
     auto lazy = in.lazy ? std::make_shared<gpu::LazyImage>(*in.lazy) : std::make_shared<gpu::LazyImage>(in.array);
@@ -42,33 +52,29 @@ void run_op(LazySample& s, const op::ImageTransformOp& op) {
         }
       }
     }
-    if (!op.fold_in(*lazy, concrete_entries)) {
+    // An image that claims padding takes no further op except more padding:
+    // compute it before the op gets to draw anything.
+    bool joined = !(lazy->extended() && !op.extends_only()) && op.fold_in(*lazy, concrete_entries);
+    if (!joined && !lazy->untouched()) {
       // the program is full: compute what we have, start a new one
-      auto pixels = (in.lazy ? *in.lazy : gpu::LazyImage(in.array)).materialise();
+      auto pixels = lazy_pixels(in);
       lazy = std::make_shared<gpu::LazyImage>(pixels);
-      if (!op.fold_in(*lazy, concrete_entries)) {
-        throw std::runtime_error("ImageTransformOp: internal error: op does not fold into an empty program");
-      }
+      joined = op.fold_in(*lazy, concrete_entries);
     }
-    out.lazy = lazy;
+    if (joined) {
+      out.lazy = lazy;
+    } else {
+      // not an op the kernels run (padding in front, a slice of the channels): the host op on the pixels
+      out.array = op.apply_key(lazy_pixels(in));
+    }
   }
   s[op.output_key()] = out;
-}
-
-std::shared_ptr<Array> concrete(const Entry& e) {
-  if (e.array) {
-    return e.array;
-  }
-  if (e.lazy->untouched()) {
-    return std::make_shared<Array>(e.lazy->source());
-  }
-  return e.lazy->materialise();
 }
 
 } // namespace
 
 Batcher::Batcher(
-    std::vector<std::shared_ptr<op::ImageTransformOp>> ops,
+    std::vector<std::shared_ptr<op::FusableOp>> ops,
     std::unordered_map<std::string, double> pad_values,
     std::unordered_map<std::string, int> batch_dims,
     std::vector<CastRequest> casts)
@@ -119,7 +125,12 @@ Sample Batcher::run(const std::vector<Sample>& raw) const {
       images.reserve(col.size());
       bool same = true;
       for (auto& e : col) {
-        images.push_back(e.lazy ? *e.lazy : gpu::LazyImage(e.array));
+        if (e.lazy && !e.lazy->extension_matches(pad)) {
+          // explicit padding with another value than the batch's: that image is computed on its own first
+          images.push_back(gpu::LazyImage(e.lazy->materialise()));
+        } else {
+          images.push_back(e.lazy ? *e.lazy : gpu::LazyImage(e.array));
+        }
         same = same && images.back().source_channels() == images.front().source_channels() &&
             images.back().is_gray() == images.front().is_gray();
       }
@@ -147,7 +158,7 @@ Sample Batcher::run(const std::vector<Sample>& raw) const {
     std::vector<std::shared_ptr<Array>> arrs;
     arrs.reserve(col.size());
     for (auto& e : col) {
-      arrs.push_back(concrete(e));
+      arrs.push_back(lazy_pixels(e));
     }
     std::shared_ptr<Array> merged =
         dim == batch_dims_.end() ? array::batch(arrs, pad) : array::batch(arrs, dim->second, pad);

@@ -31,7 +31,7 @@ struct CastRequest {
 class Batcher {
  public:
   Batcher(
-      std::vector<std::shared_ptr<op::ImageTransformOp>> ops,
+      std::vector<std::shared_ptr<op::FusableOp>> ops,
       std::unordered_map<std::string, double> pad_values,
       std::unordered_map<std::string, int> batch_dims,
       std::vector<CastRequest> casts = {});
@@ -39,14 +39,14 @@ class Batcher {
   // Empty input gives an empty sample (end of stream).
   Sample run(const std::vector<Sample>& raw) const;
 
-  const std::vector<std::shared_ptr<op::ImageTransformOp>>& ops() const { return ops_; }
+  const std::vector<std::shared_ptr<op::FusableOp>>& ops() const { return ops_; }
   const std::unordered_map<std::string, double>& pad_values() const { return pad_values_; }
   const std::unordered_map<std::string, int>& batch_dims() const { return batch_dims_; }
   const std::vector<CastRequest>& casts() const { return casts_; }
   const gpu::Placement& placement() const { return placement_; }
 
  private:
-  std::vector<std::shared_ptr<op::ImageTransformOp>> ops_;
+  std::vector<std::shared_ptr<op::FusableOp>> ops_;
   std::unordered_map<std::string, double> pad_values_;
   std::unordered_map<std::string, int> batch_dims_;
   std::vector<CastRequest> casts_;

@@ -1,6 +1,10 @@
 #include "mlx/data/gpu/Runtime.h"
 
+#include <sched.h>
+
 #include <atomic>
+#include <cctype>
+#include <cstdio>
 
 #include <algorithm>
 #include <cmath>
@@ -74,14 +78,41 @@ LazyImage LazyImage::with_source(const std::shared_ptr<const Array>& src) const 
 }
 
 int64_t LazyImage::width() const {
-  return post_.w;
+  return post_.w + ext_w_;
 }
 
 int64_t LazyImage::height() const {
-  return post_.h;
+  return post_.h + ext_h_;
 }
 
-void LazyImage::crop(int64_t x, int64_t y, int64_t w, int64_t h) {
+bool LazyImage::pad_end(int dim, int64_t amount, double value) {
+  if ((dim != 0 && dim != 1) || amount < 0) {
+    return false;
+  }
+  if (src_->type() != UInt8 || !(value >= 0.0 && value <= 255.0) || value != std::floor(value)) {
+    return false;
+  }
+  const int v = static_cast<int>(value);
+  if (extended() && v != ext_value_) {
+    return false;
+  }
+  if (amount == 0) {
+    return true;
+  }
+  (dim == 0 ? ext_h_ : ext_w_) += amount;
+  ext_value_ = v;
+  untouched_ = false;
+  return true;
+}
+
+bool LazyImage::extension_matches(double batch_pad_value) const {
+  return !extended() || static_cast<int>(static_cast<uint8_t>(static_cast<int32_t>(batch_pad_value))) == ext_value_;
+}
+
+bool LazyImage::crop(int64_t x, int64_t y, int64_t w, int64_t h) {
+  if (extended()) {
+    return false;
+  }
   if (w <= 0 || h <= 0) {
     throw std::runtime_error("image: cannot create image with 0 or negative dimension");
   }
@@ -94,19 +125,24 @@ void LazyImage::crop(int64_t x, int64_t y, int64_t w, int64_t h) {
     post_.crop(x, y, w, h);
   }
   untouched_ = false;
+  return true;
 }
 
-void LazyImage::hflip() {
+bool LazyImage::hflip() {
+  if (extended()) {
+    return false;
+  }
   if (geom_ == MLXD_GEOM_NONE) {
     pre_.flip = !pre_.flip;
   } else {
     post_.flip = !post_.flip;
   }
   untouched_ = false;
+  return true;
 }
 
 bool LazyImage::resize(int64_t dw, int64_t dh) {
-  if (geom_ != MLXD_GEOM_NONE || gray_) {
+  if (geom_ != MLXD_GEOM_NONE || gray_ || extended()) {
     return false;
   }
   if (src_->type() != UInt8) {
@@ -129,7 +165,7 @@ bool LazyImage::resize(int64_t dw, int64_t dh) {
 }
 
 bool LazyImage::affine(const float mx[6], int64_t tw, int64_t th) {
-  if (geom_ != MLXD_GEOM_NONE || gray_) {
+  if (geom_ != MLXD_GEOM_NONE || gray_ || extended()) {
     return false;
   }
   if (src_->type() != UInt8) {
@@ -148,6 +184,9 @@ bool LazyImage::affine(const float mx[6], int64_t tw, int64_t th) {
 }
 
 bool LazyImage::channel_reduction(float bias, const float m[3]) {
+  if (extended()) {
+    return false;
+  }
   if (channels() != 3) {
     throw std::runtime_error("image::channelReduction: expected a 3 channel uint8 array");
   }
@@ -194,8 +233,9 @@ void LazyImage::describe(mlxd_sample_desc& d) const {
 
 std::shared_ptr<Array> LazyImage::materialise() const {
   std::vector<LazyImage> one{*this};
-  // an image between two ops lives in host memory, like every op result of the reference
-  auto batched = Runtime::get().batch(one, 0.0, nullptr, Placement());
+  // an image between two ops lives in host memory, like every op result of the reference;
+  // the slot of this batch of one is the image with its extension, filled with the extension's value
+  auto batched = Runtime::get().batch(one, static_cast<double>(ext_value_), nullptr, Placement());
   // drop the leading batch dimension; storage is shared
   return std::make_shared<Array>(
       batched->type(), std::vector<int64_t>{batched->shape(1), batched->shape(2), batched->shape(3)},
@@ -217,6 +257,79 @@ int Runtime::device() {
     g_device = env_int("MLXD_DEVICE", env_int("LOCAL_RANK", 0));
   }
   return g_device;
+}
+
+std::pair<int, int> Runtime::bind_host_threads_to_device_node() {
+  char bus[32] = {0};
+  if (mlxd_device_pci_bus_id(device(), bus, sizeof(bus)) != MLXD_OK) {
+    return {-1, 0};
+  }
+  return bind_host_threads_to_node_of(bus, "/sys");
+}
+
+std::pair<int, int> Runtime::bind_host_threads_to_node_of(const std::string& pci_bus_id, const std::string& sysfs) {
+  std::string bus = pci_bus_id;
+  for (auto& c : bus) {
+    c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
+  }
+  auto first_line = [](const std::string& path, std::string& line) {
+    FILE* f = std::fopen(path.c_str(), "r");
+    if (!f) {
+      return false;
+    }
+    char buf[4096];
+    const bool ok = std::fgets(buf, sizeof(buf), f) != nullptr;
+    std::fclose(f);
+    if (ok) {
+      line = buf;
+      while (!line.empty() && (line.back() == '\n' || line.back() == ' ')) {
+        line.pop_back();
+      }
+    }
+    return ok && !line.empty();
+  };
+  std::string text;
+  if (!first_line(sysfs + "/bus/pci/devices/" + bus + "/numa_node", text)) {
+    return {-1, 0};
+  }
+  const int node = std::atoi(text.c_str());
+  if (node < 0) {
+    return {-1, 0};
+  }
+  // "0-15,64-79": the node's CPUs, intersected with what this process may use
+  std::string list;
+  if (!first_line(sysfs + "/devices/system/node/node" + std::to_string(node) + "/cpulist", list)) {
+    return {-1, 0};
+  }
+  cpu_set_t allowed, want;
+  CPU_ZERO(&allowed);
+  CPU_ZERO(&want);
+  if (sched_getaffinity(0, sizeof(allowed), &allowed) != 0) {
+    return {-1, 0};
+  }
+  int kept = 0;
+  size_t at = 0;
+  while (at < list.size()) {
+    size_t end = list.find(',', at);
+    if (end == std::string::npos) {
+      end = list.size();
+    }
+    const std::string part = list.substr(at, end - at);
+    const size_t dash = part.find('-');
+    const int lo = std::atoi(part.c_str());
+    const int hi = dash == std::string::npos ? lo : std::atoi(part.c_str() + dash + 1);
+    for (int c = lo; c <= hi && c < CPU_SETSIZE; c++) {
+      if (c >= 0 && CPU_ISSET(c, &allowed)) {
+        CPU_SET(c, &want);
+        kept++;
+      }
+    }
+    at = end + 1;
+  }
+  if (kept == 0 || sched_setaffinity(0, sizeof(want), &want) != 0) {
+    return {node, 0};
+  }
+  return {node, kept};
 }
 
 void Runtime::check(int rc) const {

@@ -9,6 +9,7 @@
 #include <condition_variable>
 #include <mutex>
 #include <map>
+#include <utility>
 #include <vector>
 
 #include "mlx/data/Array.h"
@@ -62,14 +63,25 @@ class LazyImage {
   // The same program on another source of the same shape (the frames of a clip).
   LazyImage with_source(const std::shared_ptr<const Array>& src) const;
 
-  void crop(int64_t x, int64_t y, int64_t w, int64_t h);
-  void hflip();
-  // These return false when the op cannot join the program already recorded
-  // (a second geometric op, or a geometric op after the channel reduction);
-  // the caller then materialises and starts a new LazyImage.
+  // Every op returns false when it cannot join the program already recorded
+  // (a second geometric op, a geometric op after the channel reduction, any
+  // op after an extension); the caller then materialises and starts a new
+  // LazyImage.
+  bool crop(int64_t x, int64_t y, int64_t w, int64_t h);
+  bool hflip();
   bool resize(int64_t dw, int64_t dh);
   bool affine(const float mx[6], int64_t tw, int64_t th);
   bool channel_reduction(float bias, const float m[3]);
+
+  // Explicit padding at the end of the rows (dim 0) or columns (dim 1):
+  // `amount` more of them holding `value`.  Nothing is computed for it - the
+  // image only claims a larger rectangle of its batch slot, which the kernel
+  // fills with the batch's pad value; so the batch node checks that the two
+  // values agree (extension_matches) and materialises the image when not.
+  // False for another dimension, a value that is no uint8, or a second value.
+  bool pad_end(int dim, int64_t amount, double value);
+  bool extended() const { return ext_w_ > 0 || ext_h_ > 0; }
+  bool extension_matches(double batch_pad_value) const;
 
   void describe(mlxd_sample_desc& d) const;
   void gray_params(int32_t m[3], int32_t& bias) const;
@@ -88,6 +100,8 @@ class LazyImage {
   int32_t gray_m_[3] = {0, 0, 0};
   int32_t gray_bias_ = 0;
   bool untouched_ = true;
+  int64_t ext_w_ = 0, ext_h_ = 0;   // columns / rows claimed beyond the program's output
+  int ext_value_ = 0;
 };
 
 class Runtime {
@@ -98,6 +112,17 @@ class Runtime {
   // MLXD_DEVICE, then LOCAL_RANK, then 0).
   static void set_device(int device);
   static int device();
+
+  // Keep the calling thread - and every thread it starts afterwards, the
+  // pipeline's workers included - on the CPUs of the NUMA node the selected
+  // GPU hangs off, so that page-locked blocks are allocated in that node's
+  // memory and copies do not cross the socket interconnect.  Call it before the
+  // first pipeline is built.  Returns {node, cpus kept}; {-1, 0} and no change
+  // when the node cannot be read (no sysfs entry, single-node machine).
+  static std::pair<int, int> bind_host_threads_to_device_node();
+  // The same for a PCI address ("0000:1b:00.0", any case) looked up under a
+  // sysfs tree; the tests point it at a made-up tree.
+  static std::pair<int, int> bind_host_threads_to_node_of(const std::string& pci_bus_id, const std::string& sysfs);
 
   mlxd_ctx* ctx();
   // Check a lane out for one call in flight (blocks while all are busy) and

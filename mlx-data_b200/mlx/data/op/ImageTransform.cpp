@@ -129,8 +129,7 @@ bool ImageCenterCrop::fold(gpu::LazyImage& image) const {
   if (h_ > h || w_ > w) {
     throw std::runtime_error("ImageCenterCrop: target image size larger than input image");
   }
-  image.crop((w - w_) / 2, (h - h_) / 2, w_, h_);
-  return true;
+  return image.crop((w - w_) / 2, (h - h_) / 2, w_, h_);
 }
 
 bool ImageRandomCrop::fold(gpu::LazyImage& image) const {
@@ -145,8 +144,7 @@ bool ImageRandomCrop::fold(gpu::LazyImage& image) const {
   std::uniform_int_distribution<int64_t> draw_y{0, h - h_};
   const int64_t x = draw_x(state->randomGenerator);
   const int64_t y = draw_y(state->randomGenerator);
-  image.crop(x, y, w_, h_);
-  return true;
+  return image.crop(x, y, w_, h_);
 }
 
 ImageRandomAreaCrop::ImageRandomAreaCrop(
@@ -237,8 +235,7 @@ bool ImageRandomAreaCrop::fold(gpu::LazyImage& image) const {
   if (r.tw == 0 || r.th == 0) {
     return true;  // image unchanged
   }
-  image.crop(r.tx, r.ty, r.tw, r.th);
-  return true;
+  return image.crop(r.tx, r.ty, r.tw, r.th);
 }
 
 // ------------------------------------------------------------ flip
@@ -246,7 +243,7 @@ bool ImageRandomHFlip::fold(gpu::LazyImage& image) const {
   auto state = core::get_state();
   std::uniform_real_distribution<float> unit{0, 1.0};
   if (unit(state->randomGenerator) <= prob_) {
-    image.hflip();
+    return image.hflip();
   }
   return true;
 }

@@ -18,23 +18,13 @@ namespace mlx {
 namespace data {
 namespace op {
 
-class ImageTransformOp : public KeyTransformOp {
+class ImageTransformOp : public FusableOp {
  public:
-  ImageTransformOp(const std::string& ikey, const std::string& okey = "") : KeyTransformOp(ikey, okey) {}
+  ImageTransformOp(const std::string& ikey, const std::string& okey = "") : FusableOp(ikey, okey) {}
   Sample apply(const Sample& sample) const override;
   std::shared_ptr<Array> apply_key(const std::shared_ptr<const Array>& src) const override;
   virtual std::shared_ptr<Array> apply_image(const std::shared_ptr<const Array>& image) const;
   virtual std::shared_ptr<Array> apply_video(const std::shared_ptr<const Array>& video) const;
-  // Record this op on `image`.  Returns false when it cannot join the program
-  // already recorded; the caller materialises the image and folds again.
-  virtual bool fold(gpu::LazyImage& image) const = 0;
-  // fold() for ops whose parameters may come from other entries of the sample
-  // (`sample` holds the entries that are concrete arrays).
-  virtual bool fold_in(gpu::LazyImage& image, const Sample& sample) const {
-    (void)sample;
-    return fold(image);
-  }
-  virtual bool reads_sample() const { return false; }
 
  private:
   // A clip [F, H, W, C]: the op is recorded once, on the first frame - so random

@@ -1,5 +1,7 @@
 // slice / random_slice (mlx/data/op/Slice.cpp:12-86): host-side sub-array ops
-// on any array type; they end a run of fusable image ops.
+// on any array type.  Under a batch node a slice of the rows and columns of a
+// uint8 image is a crop and joins the fused run; a slice that touches the
+// channel dimension is computed on the host.
 #pragma once
 
 #include <algorithm>
@@ -8,6 +10,7 @@
 #include <vector>
 
 #include "mlx/data/core/State.h"
+#include "mlx/data/gpu/Runtime.h"
 #include "mlx/data/op/KeyTransform.h"
 
 namespace mlx {
@@ -15,11 +18,11 @@ namespace data {
 namespace op {
 
 // [starts[i], ends[i]) along dims[i], clipped to the array's extent.
-class Slice : public KeyTransformOp {
+class Slice : public FusableOp {
  public:
   Slice(const std::string& ikey, std::vector<int> dims, std::vector<int64_t> starts, std::vector<int64_t> ends,
         const std::string& okey = "")
-      : KeyTransformOp(ikey, okey), dims_(std::move(dims)), starts_(std::move(starts)), ends_(std::move(ends)) {
+      : FusableOp(ikey, okey), dims_(std::move(dims)), starts_(std::move(starts)), ends_(std::move(ends)) {
     if (dims_.size() != starts_.size() || dims_.size() != ends_.size()) {
       throw std::invalid_argument("Slice: number of dims much match provided starts and ends");
     }
@@ -34,6 +37,27 @@ class Slice : public KeyTransformOp {
     }
     return array::sub(src, std::move(offsets), std::move(shape));
   }
+  bool fold(gpu::LazyImage& image) const override {
+    if (image.extended()) {
+      return false;
+    }
+    int64_t off[2] = {0, 0};
+    int64_t len[2] = {image.height(), image.width()};
+    for (size_t i = 0; i < dims_.size(); i++) {
+      const int d = dims_[i] < 0 ? dims_[i] + 3 : dims_[i];
+      if (d != 0 && d != 1) {
+        return false;
+      }
+      off[d] = starts_[i];
+      len[d] = std::min(len[d] - starts_[i], ends_[i] - starts_[i]);
+    }
+    // anything the sub-array code would refuse is left to it, with its messages
+    if (off[0] < 0 || off[1] < 0 || len[0] <= 0 || len[1] <= 0 || off[0] + len[0] > image.height() ||
+        off[1] + len[1] > image.width()) {
+      return false;
+    }
+    return image.crop(off[1], off[0], len[1], len[0]);
+  }
 
  private:
   std::vector<int> dims_;
@@ -42,10 +66,10 @@ class Slice : public KeyTransformOp {
 
 // A window of sizes[i] along dims[i] at a uniformly random offset (one double
 // draw per listed dimension that is longer than its window, in list order).
-class RandomSlice : public KeyTransformOp {
+class RandomSlice : public FusableOp {
  public:
   RandomSlice(const std::string& ikey, std::vector<int> dims, std::vector<int64_t> sizes, const std::string& okey = "")
-      : KeyTransformOp(ikey, okey), dims_(std::move(dims)), sizes_(std::move(sizes)) {
+      : FusableOp(ikey, okey), dims_(std::move(dims)), sizes_(std::move(sizes)) {
     if (dims_.size() != sizes_.size()) {
       throw std::invalid_argument("RandomSlice: number of dims much match provided sizes");
     }
@@ -64,6 +88,31 @@ class RandomSlice : public KeyTransformOp {
       }
     }
     return array::sub(src, std::move(offsets), std::move(shape));
+  }
+  bool fold(gpu::LazyImage& image) const override {
+    // decide before anything is drawn: a refusal must leave the generator alone
+    if (image.extended()) {
+      return false;
+    }
+    for (size_t i = 0; i < dims_.size(); i++) {
+      const int d = dims_[i] < 0 ? dims_[i] + 3 : dims_[i];
+      if ((d != 0 && d != 1) || sizes_[i] <= 0) {
+        return false;
+      }
+    }
+    std::uniform_real_distribution<> draw(0.0, 1.0);
+    int64_t off[2] = {0, 0};
+    int64_t len[2] = {image.height(), image.width()};
+    auto state = core::get_state();
+    for (size_t i = 0; i < dims_.size(); i++) {
+      const int d = dims_[i] < 0 ? dims_[i] + 3 : dims_[i];
+      const int64_t room = len[d] - sizes_[i];
+      if (room > 0) {
+        len[d] = sizes_[i];
+        off[d] = static_cast<int64_t>((room + 1) * draw(state->randomGenerator));
+      }
+    }
+    return image.crop(off[1], off[0], len[1], len[0]);
   }
 
  private:

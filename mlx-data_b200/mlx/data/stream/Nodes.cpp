@@ -49,17 +49,17 @@ Sample Transform::next() const {
 // ------------------------------------------------------------ Batch
 namespace {
 std::shared_ptr<Stream> peel_image_ops(
-    const std::shared_ptr<Stream>& top, std::vector<std::shared_ptr<op::ImageTransformOp>>& ops) {
+    const std::shared_ptr<Stream>& top, std::vector<std::shared_ptr<op::FusableOp>>& ops) {
   std::shared_ptr<Stream> cur = top;
-  std::vector<std::vector<std::shared_ptr<op::ImageTransformOp>>> layers;
+  std::vector<std::vector<std::shared_ptr<op::FusableOp>>> layers;
   for (;;) {
     auto t = std::dynamic_pointer_cast<Transform>(cur);
     if (!t || t->ops().empty()) {
       break;
     }
-    std::vector<std::shared_ptr<op::ImageTransformOp>> mine;
+    std::vector<std::shared_ptr<op::FusableOp>> mine;
     for (auto& o : t->ops()) {
-      if (auto io = std::dynamic_pointer_cast<op::ImageTransformOp>(o)) {
+      if (auto io = std::dynamic_pointer_cast<op::FusableOp>(o)) {
         mine.push_back(io);
       }
     }
@@ -85,7 +85,7 @@ Batch::Batch(
   if (batch_size <= 0) {
     throw std::runtime_error("Batch: batch size must be positive");
   }
-  std::vector<std::shared_ptr<op::ImageTransformOp>> ops;
+  std::vector<std::shared_ptr<op::FusableOp>> ops;
   base_ = peel_image_ops(source, ops);
   batcher_ = std::make_shared<core::Batcher>(ops, pad_values, batch_dims);
 }

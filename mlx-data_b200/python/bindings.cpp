@@ -614,6 +614,15 @@ PYBIND11_MODULE(_c, m) {
   core.def("set_device", &gpu::Runtime::set_device, py::arg("device"),
            "Choose the CUDA device; call before the first op runs.");
   core.def("device", &gpu::Runtime::device);
+  core.def("bind_host_threads_to_device_node",
+           []() {
+             const auto r = gpu::Runtime::bind_host_threads_to_device_node();
+             return py::make_tuple(r.first, r.second);
+           },
+           "Keep this thread, and the threads started from it afterwards (the pipeline's workers), on the CPUs of "
+           "the NUMA node the selected GPU is attached to, so page-locked buffers land in that node's memory.  "
+           "Call it after set_device and before building pipelines.  Returns (node, cpus kept); (-1, 0) when the "
+           "machine does not say.");
   core.def("pinned_empty",
            [](const std::vector<int64_t>& shape, const std::string& dtype) {
              const py::dtype dt(dtype);
@@ -623,6 +632,13 @@ PYBIND11_MODULE(_c, m) {
            py::arg("shape"), py::arg("dtype") = "uint8",
            "A numpy array in page-locked host memory: samples stored in such arrays are copied to the "
            "GPU asynchronously at full PCIe speed.");
+  core.def("bind_host_threads_to_node_of",
+           [](const std::string& pci_bus_id, const std::string& sysfs) {
+             const auto r = gpu::Runtime::bind_host_threads_to_node_of(pci_bus_id, sysfs);
+             return py::make_tuple(r.first, r.second);
+           },
+           py::arg("pci_bus_id"), py::arg("sysfs") = "/sys",
+           "bind_host_threads_to_device_node for a given PCI address and sysfs tree.");
   core.def("set_rgba_resize_independent", &gpu::Runtime::set_rgba_resize_independent, py::arg("accept"),
            "Resizing 4-channel images: mlx-data weights colour by alpha while filtering, this library filters the "
            "four channels independently, so results differ where alpha varies.  The resize ops refuse 4-channel "
