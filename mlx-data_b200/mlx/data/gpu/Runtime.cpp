@@ -416,31 +416,32 @@ Placement Runtime::placement() const {
   return defaults_;
 }
 
-void* Runtime::pool_take(Pool& pool, size_t bytes, size_t& held) {
+bool Runtime::pool_take(Pool& pool, size_t bytes, size_t& held, Block& out) {
   std::lock_guard<std::mutex> g(mu_);
   auto it = pool.blocks.lower_bound(bytes);
   // reuse a block that is at most 25% larger than asked for
   if (it != pool.blocks.end() && it->first <= bytes + bytes / 4) {
-    void* p = it->second;
+    out = it->second;
     held = it->first;
     pool.bytes -= it->first;
     pool.blocks.erase(it);
-    return p;
+    return true;
   }
-  return nullptr;
+  return false;
 }
 
-bool Runtime::pool_give(Pool& pool, void* p, size_t bytes) {
+bool Runtime::pool_give(Pool& pool, const Block& b, size_t bytes) {
   std::lock_guard<std::mutex> g(mu_);
   if (pool.bytes + bytes <= pool.limit) {
-    pool.blocks.emplace(bytes, p);
+    pool.blocks.emplace(bytes, b);
     pool.bytes += bytes;
     return true;
   }
   return false;
 }
 
-std::shared_ptr<Array> Runtime::pooled_array(ArrayType type, const std::vector<int64_t>& shape, bool on_device) {
+std::shared_ptr<Array> Runtime::pooled_array(
+    ArrayType type, const std::vector<int64_t>& shape, bool on_device, const void* const* queued_on) {
   mlxd_ctx* c = ctx();
   int64_t n = array_type_size(type);
   for (auto d : shape) {
@@ -450,19 +451,32 @@ std::shared_ptr<Array> Runtime::pooled_array(ArrayType type, const std::vector<i
   bytes = (bytes + 4095) & ~size_t(4095);
   Pool& pool = on_device ? device_pool_ : pinned_pool_;
   size_t held = bytes;  // a recycled block goes back under the size it was allocated with
-  void* p = pool_take(pool, bytes, held);
-  if (!p) {
-    p = on_device ? mlxd_device_alloc(c, bytes) : mlxd_pinned_alloc(bytes);
-    if (!p) {
+  Block blk{nullptr, false, nullptr};
+  if (pool_take(pool, bytes, held, blk)) {
+    // Work queued on a caller's stream may still use the block (the kernel
+    // that filled it, the caller's consumers queued before it was dropped).
+    // The same stream orders itself; anyone else waits for that stream.
+    if (blk.tagged && !(queued_on && *queued_on == blk.stream)) {
+      int32_t word = 0;
+      const int rc = mlxd_stream_status(c, blk.stream, &word);
+      if (rc != MLXD_OK) {
+        pool_give(pool, blk, held);
+        check(rc);
+      }
+    }
+  } else {
+    blk.p = on_device ? mlxd_device_alloc(c, bytes) : mlxd_pinned_alloc(bytes);
+    if (!blk.p) {
       throw std::runtime_error(std::string("mlx-data GPU path: ") + mlxd_last_error());
     }
   }
   Runtime* self = this;
-  std::shared_ptr<void> storage(p, [self, held, on_device, c](void* q) {
-    Pool& back = on_device ? self->device_pool_ : self->pinned_pool_;
-    if (!self->pool_give(back, q, held)) {
+  const Block back{blk.p, queued_on != nullptr, queued_on ? const_cast<void*>(*queued_on) : nullptr};
+  std::shared_ptr<void> storage(blk.p, [self, held, on_device, c, back](void* q) {
+    Pool& to = on_device ? self->device_pool_ : self->pinned_pool_;
+    if (!self->pool_give(to, back, held)) {
       if (on_device) {
-        mlxd_device_free(c, q);
+        mlxd_device_free(c, q);   // cudaFree waits for the device
       } else {
         mlxd_pinned_free(q);
       }
@@ -472,11 +486,12 @@ std::shared_ptr<Array> Runtime::pooled_array(ArrayType type, const std::vector<i
 }
 
 std::shared_ptr<Array> Runtime::pinned_array(ArrayType type, const std::vector<int64_t>& shape) {
-  return pooled_array(type, shape, false);
+  return pooled_array(type, shape, false, nullptr);
 }
 
-std::shared_ptr<Array> Runtime::device_array(ArrayType type, const std::vector<int64_t>& shape) {
-  return pooled_array(type, shape, true);
+std::shared_ptr<Array> Runtime::device_array(
+    ArrayType type, const std::vector<int64_t>& shape, const void* const* queued_on) {
+  return pooled_array(type, shape, true, queued_on);
 }
 
 std::shared_ptr<Array> Runtime::batch(
@@ -530,10 +545,13 @@ std::shared_ptr<Array> Runtime::batch(
     std::memcpy(b.std_, cast->std_, sizeof(b.std_));
   }
   const std::vector<int64_t> shape{n, max_h, max_w, first.channels()};
-  auto out = dst_dev ? device_array(out_type, shape) : pinned_array(out_type, shape);
+  const bool on_callers_stream = src_dev && dst_dev && where.use_stream;
+  const void* callers_stream = where.stream;
+  auto out = dst_dev ? device_array(out_type, shape, on_callers_stream ? &callers_stream : nullptr)
+                     : pinned_array(out_type, shape);
   b.dst = out->data();
   mlxd_ctx* c = ctx();
-  if (src_dev && dst_dev && where.use_stream) {
+  if (on_callers_stream) {
     // everything stays on the GPU: queue on the caller's stream and return
     check(mlxd_fused_batch_on_stream(c, where.stream, descs.data(), n, &b));
     return out;

@@ -134,7 +134,12 @@ class Runtime {
   // Array whose storage is page-locked host memory from a recycling pool.
   std::shared_ptr<Array> pinned_array(ArrayType type, const std::vector<int64_t>& shape);
   // Array whose storage is memory of the context's GPU, from a recycling pool.
-  std::shared_ptr<Array> device_array(ArrayType type, const std::vector<int64_t>& shape);
+  // `queued_on`, when given, is the caller-owned stream on which work that
+  // writes (and later reads) the block is queued without being waited for:
+  // the block goes back to the pool tagged with it, and whoever takes it for
+  // another stream waits for that stream first.
+  std::shared_ptr<Array> device_array(
+      ArrayType type, const std::vector<int64_t>& shape, const void* const* queued_on = nullptr);
 
   // Where batch() and cast() leave their results: host (default, what
   // mlx-data does) or the GPU's memory, for consumers that train on that GPU.
@@ -167,14 +172,20 @@ class Runtime {
 
  private:
   Runtime() = default;
+  struct Block {
+    void* p;
+    bool tagged;      // last used by work queued on `stream` that nobody waited for
+    void* stream;
+  };
   struct Pool {
-    std::multimap<size_t, void*> blocks;
+    std::multimap<size_t, Block> blocks;
     size_t bytes = 0;
     size_t limit = size_t(16) << 30;
   };
-  void* pool_take(Pool& pool, size_t bytes, size_t& held);
-  bool pool_give(Pool& pool, void* p, size_t bytes);
-  std::shared_ptr<Array> pooled_array(ArrayType type, const std::vector<int64_t>& shape, bool on_device);
+  bool pool_take(Pool& pool, size_t bytes, size_t& held, Block& out);
+  bool pool_give(Pool& pool, const Block& b, size_t bytes);
+  std::shared_ptr<Array> pooled_array(
+      ArrayType type, const std::vector<int64_t>& shape, bool on_device, const void* const* queued_on);
   Pool device_pool_;
   Placement defaults_;          // guarded by mu_
 

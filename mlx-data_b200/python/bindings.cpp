@@ -653,7 +653,9 @@ PYBIND11_MODULE(_c, m) {
            py::arg("cuda_stream"), py::arg("enabled") = true,
            "Default for batch nodes built from now on: queue GPU-to-GPU work (GPU-resident samples and device "
            "output) on this CUDA stream handle without waiting for it; enabled=False goes back to the internal "
-           "lanes.  A pipeline keeps the setting it was built with.");
+           "lanes.  A pipeline keeps the setting it was built with.  GPU-resident samples must have been "
+           "written by work on this stream (or be complete); without a stream set, the internal lanes read "
+           "them as they are, so they must be complete before the pipeline pulls them.");
   core.def("stream_status",
            [](uintptr_t stream) {
              int32_t word = 0;
