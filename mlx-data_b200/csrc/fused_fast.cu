@@ -20,9 +20,6 @@
 #include "fused_batch.h"
 #include "kernel_common.cuh"
 
-#ifndef MLXD_COPY_ISSUE
-#define MLXD_COPY_ISSUE 0
-#endif
 namespace mlxd {
 namespace {
 
@@ -63,14 +60,6 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
 }
 
 // 16-byte aligned global -> shared bulk copy, bytes a multiple of 16.
-// True in exactly one lane of a converged warp.
-__device__ __forceinline__ bool elect_one() {
-  unsigned pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-  return pred != 0;
-}
-
 __device__ __forceinline__ void bulk_copy(unsigned dst_smem, const void* src_gmem, unsigned bytes, unsigned bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
@@ -400,7 +389,6 @@ __device__ __forceinline__ void start_pass(
     const Axis& ax, int nr, int rlo, int rows) {
   const int tid = threadIdx.x;
   const size_t src_pitch = (size_t)s.src_w * C;
-#if MLXD_COPY_ISSUE == 0
   if (tid < rows) {
     const uintptr_t ga = reinterpret_cast<uintptr_t>(g.g0) + (size_t)tid * src_pitch;
     const int phase = (int)(ga & 15);
@@ -408,27 +396,6 @@ __device__ __forceinline__ void start_pass(
     mbar_expect_tx(sm.bar, len);
     bulk_copy(sm.srct + (unsigned)(tid * g.pitch_s), reinterpret_cast<const void*>(ga - phase), len, sm.bar);
   }
-#else
-  // A loop whose values are the same in every lane of the warp, with one
-  // elected lane issuing: the copy's operands then live in uniform registers
-  // from the start instead of being moved there lane by lane.
-  {
-#if MLXD_COPY_ISSUE == 1
-    const int first = tid >> 5, step = kThreads >> 5;          // rows dealt over the warps
-#else
-    const int first = (tid >> 5) == 0 ? 0 : rows, step = 1;    // warp 0 issues all of them
-#endif
-    for (int r = first; r < rows; r += step) {
-      const uintptr_t ga = reinterpret_cast<uintptr_t>(g.g0) + (size_t)r * src_pitch;
-      const int phase = (int)(ga & 15);
-      const unsigned len = (unsigned)((phase + g.wbytes + 15) & ~15);
-      if (elect_one()) {
-        mbar_expect_tx(sm.bar, len);
-        bulk_copy(sm.srct + (unsigned)(r * g.pitch_s), reinterpret_cast<const void*>(ga - phase), len, sm.bar);
-      }
-    }
-  }
-#endif
   // horizontal taps: one thread per output column (the last warps, which issue
   // no copies); every weight is stored twice, side by side, so the packed
   // multiply-add reads its (w, w) operand with one 64-bit load
