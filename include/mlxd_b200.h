@@ -138,8 +138,11 @@ MLXD_API const char* mlxd_last_error(void);
  * source of a host-fed mlxd_fused_batch lies in such blocks, a kernel reads
  * just the rectangle each chain needs over the bus (for a centre crop of a
  * 1080 x 1920 frame that is 57 % of the bytes a row-contiguous copy moves);
- * other host memory goes through the copy engines.  MLXD_HOST_GATHER=0 in the
- * environment turns the kernel path off. */
+ * page-locked memory that did not come from here goes through the copy engines,
+ * and sources in ordinary (pageable) memory are first packed - needed rectangle
+ * only - into a page-locked block of the lane by the calling thread and up to
+ * MLXD_PACK_THREADS - 1 helpers (default 4 threads in all), then copied once
+ * per batch.  MLXD_HOST_GATHER=0 in the environment turns the kernel path off. */
 MLXD_API void* mlxd_pinned_alloc(size_t bytes);
 MLXD_API void mlxd_pinned_free(void* p);
 

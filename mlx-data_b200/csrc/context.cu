@@ -3,6 +3,7 @@
 
 #include <map>
 
+#include <atomic>
 #include <chrono>
 #include <cmath>
 #include <cstdlib>
@@ -429,6 +430,17 @@ int prepare_launch(
   return MLXD_OK;
 }
 
+// Threads that pack one batch's pageable sources (the caller included):
+// MLXD_PACK_THREADS, default 4, at most 32.
+static int pack_threads() {
+  static const int n = [] {
+    const char* v = std::getenv("MLXD_PACK_THREADS");
+    const int want = v && *v ? std::atoi(v) : 4;
+    return want < 1 ? 1 : (want > 32 ? 32 : want);
+  }();
+  return n;
+}
+
 int enqueue_on_lane(
     mlxd_ctx* ctx, Lane& lane, const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* batch,
     const std::vector<void*>* per_sample_dst) {
@@ -614,19 +626,35 @@ int enqueue_on_lane(
     }
     MLXD_CUDA(cudaEventSynchronize(lane.src_copied));
     const auto t0 = std::chrono::steady_clock::now();
-    for (int i = 0; i < n; i++) {
-      if (direct_copy[i]) {
-        continue;
-      }
-      uint8_t* to = static_cast<uint8_t*>(lane.h_src.ptr) + pieces[i].offset;
-      const uint8_t* from = pieces[i].from;
-      if (pieces[i].row_bytes == pieces[i].from_pitch) {
-        std::memcpy(to, from, pieces[i].row_bytes * pieces[i].rows);
-      } else {
-        for (size_t r = 0; r < pieces[i].rows; r++) {
-          std::memcpy(to + r * pieces[i].row_bytes, from + r * pieces[i].from_pitch, pieces[i].row_bytes);
+    // The calling thread and up to pack_threads - 1 helpers started for this
+    // batch take samples off a shared counter; packing is plain row copies.
+    std::atomic<int> next{0};
+    uint8_t* const block = static_cast<uint8_t*>(lane.h_src.ptr);
+    auto pack = [&]() {
+      for (int i = next.fetch_add(1); i < n; i = next.fetch_add(1)) {
+        if (direct_copy[i]) {
+          continue;
+        }
+        uint8_t* to = block + pieces[i].offset;
+        const uint8_t* from = pieces[i].from;
+        if (pieces[i].row_bytes == pieces[i].from_pitch) {
+          std::memcpy(to, from, pieces[i].row_bytes * pieces[i].rows);
+        } else {
+          for (size_t r = 0; r < pieces[i].rows; r++) {
+            std::memcpy(to + r * pieces[i].row_bytes, from + r * pieces[i].from_pitch, pieces[i].row_bytes);
+          }
         }
       }
+    };
+    const int helpers = stage_bytes >= (size_t(8) << 20) ? std::min(pack_threads() - 1, n - 1) : 0;
+    std::vector<std::thread> crew;
+    crew.reserve(helpers > 0 ? helpers : 0);
+    for (int t = 0; t < helpers; t++) {
+      crew.emplace_back(pack);
+    }
+    pack();
+    for (auto& th : crew) {
+      th.join();
     }
     ctx->host_stage_ns += (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(
         std::chrono::steady_clock::now() - t0).count();
