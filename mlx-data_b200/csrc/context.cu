@@ -237,9 +237,6 @@ int plan_one_sample(
         if (rc != MLXD_OK) {
           return rc;
         }
-        if (s.pre_flip) {
-          need.needs_generic = 1;
-        }
       }
     } else if (d.geom == MLXD_GEOM_AFFINE) {
       s.mode = kModeAffine;

@@ -72,7 +72,7 @@ struct PassNeed {
   int32_t mid_float4s;
   int32_t weight_floats;
   int32_t u_cap;
-  int32_t needs_generic;      // a sample only the generic kernel handles (mirrored source under a resize)
+  int32_t needs_generic;      // a sample only the generic kernel handles (none at present)
 };
 
 // Bytes of dynamic shared memory the kernel needs for these parameters.

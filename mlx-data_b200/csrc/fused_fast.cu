@@ -364,8 +364,17 @@ __device__ __forceinline__ PassGeom pass_geom(const DevSample& s, const Axis& ax
   int f0, l0, f1, l1;
   axis_range(ax, bx, f0, l0);
   axis_range(ax, bx + nc - 1, f1, l1);
-  g.clo = clampi(f0, 0, s.pre_w - 1);
-  const int chi = clampi(l1, 0, s.pre_w - 1);
+  // f0 .. l1 are columns of the window as the filter sees it; with a mirrored
+  // source they are staged from the mirrored positions (the vertical pass does
+  // not care, the horizontal pass walks the planes right to left)
+  int alo = clampi(f0, 0, s.pre_w - 1);
+  int chi = clampi(l1, 0, s.pre_w - 1);
+  if (s.pre_flip) {
+    const int t = alo;
+    alo = s.pre_w - 1 - chi;
+    chi = s.pre_w - 1 - t;
+  }
+  g.clo = alo;
   g.edge_x = f0 < 0 || l1 > s.pre_w - 1;
   g.ncols = chi - g.clo + 1;
   g.wbytes = g.ncols * C;
@@ -657,25 +666,44 @@ __device__ void resize_rows(
           cb[c] = col_a + (unsigned)c * plane;
         }
         if (!cur.edge_x) {
-          int col = PlanePad<C>::value + f - cur.clo;
-          while (wq != wq_end) {
-            const f32x2 wk = lds_u64<0>(wq);
-            const unsigned off = (unsigned)skew(col) * 16u;
+          // two copies of the tap loop, so that the usual one keeps its constant step
+          if (!s.pre_flip) {
+            int col = PlanePad<C>::value + f - cur.clo;
+            while (wq != wq_end) {
+              const f32x2 wk = lds_u64<0>(wq);
+              const unsigned off = (unsigned)skew(col) * 16u;
 #pragma unroll
-            for (int c = 0; c < C; c++) {
-              f32x2 v01, v23;
-              lds_v2u64<0>(cb[c] + off, v01, v23);
-              ffma2(acc[c][0], v01, wk);
-              ffma2(acc[c][1], v23, wk);
+              for (int c = 0; c < C; c++) {
+                f32x2 v01, v23;
+                lds_v2u64<0>(cb[c] + off, v01, v23);
+                ffma2(acc[c][0], v01, wk);
+                ffma2(acc[c][1], v23, wk);
+              }
+              col++;
+              wq += 8;
             }
-            col++;
-            wq += 8;
+          } else {
+            int col = PlanePad<C>::value + (s.pre_w - 1 - f) - cur.clo;
+            while (wq != wq_end) {
+              const f32x2 wk = lds_u64<0>(wq);
+              const unsigned off = (unsigned)skew(col) * 16u;
+#pragma unroll
+              for (int c = 0; c < C; c++) {
+                f32x2 v01, v23;
+                lds_v2u64<0>(cb[c] + off, v01, v23);
+                ffma2(acc[c][0], v01, wk);
+                ffma2(acc[c][1], v23, wk);
+              }
+              col--;
+              wq += 8;
+            }
           }
         } else {
           for (int k = 0; wq != wq_end; k++) {
             const f32x2 wk = lds_u64<0>(wq);
+            const int seen = clampi(f + k, 0, s.pre_w - 1);
             const unsigned off =
-                (unsigned)skew(PlanePad<C>::value + clampi(f + k, 0, s.pre_w - 1) - cur.clo) * 16u;
+                (unsigned)skew(PlanePad<C>::value + (s.pre_flip ? s.pre_w - 1 - seen : seen) - cur.clo) * 16u;
 #pragma unroll
             for (int c = 0; c < C; c++) {
               f32x2 v01, v23;

@@ -277,6 +277,23 @@ FAST_RESIZE_CASES = [
     ((240, 320), 3, [("image_resize_smallest_side", dict(key="image", size=96)),
                      ("image_random_h_flip", dict(key="image", prob=1.0)),
                      ("image_center_crop", dict(key="image", w=80, h=80))]),
+    # mirrored sources: the flip comes before the resize
+    ((97, 131), 3, [("image_random_h_flip", dict(key="image", prob=1.0)),
+                    ("image_resize", dict(key="image", w=33, h=29))]),
+    ((96, 128), 1, [("image_random_h_flip", dict(key="image", prob=1.0)),
+                    ("image_center_crop", dict(key="image", w=101, h=77)),
+                    ("image_resize", dict(key="image", w=160, h=120))]),
+    ((513, 777), 3, [("image_random_h_flip", dict(key="image", prob=1.0)),
+                     ("image_random_crop", dict(key="image", w=701, h=451)),
+                     ("image_resize", dict(key="image", w=90, h=70)),
+                     ("image_random_h_flip", dict(key="image", prob=1.0)),
+                     ("image_center_crop", dict(key="image", w=77, h=63))]),
+    ((5, 3), 3, [("image_random_h_flip", dict(key="image", prob=1.0)),
+                 ("image_resize", dict(key="image", w=67, h=130))]),
+    ((700, 1100), 4, [("image_random_h_flip", dict(key="image", prob=1.0)),
+                      ("image_resize", dict(key="image", w=37, h=25))]),
+    ((300, 410), 3, [("image_random_h_flip", dict(key="image", prob=0.5)),
+                     ("image_resize_smallest_side", dict(key="image", size=128))]),
 ]
 
 
