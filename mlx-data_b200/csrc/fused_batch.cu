@@ -453,7 +453,7 @@ cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream) {
 
 void choose_kernel(LaunchParams& p, const PassNeed& need) {
   const bool channels_ok = p.c_in == 1 || p.c_in == 3 || p.c_in == 4;
-  p.use_fast = (p.out_f32 && !p.gray && channels_ok && !need.needs_generic) ? 1 : 0;
+  p.use_fast = (p.out_f32 && channels_ok && !need.needs_generic) ? 1 : 0;
 }
 
 AxisPlan plan_axis(int32_t n_src, int32_t n_dst, int32_t sub) {

@@ -275,6 +275,16 @@ __device__ __forceinline__ void vertical_taps(unsigned up, unsigned wp, unsigned
   }
 }
 
+// Channel reduction of one quantised pixel: 16.16 fixed point, truncating
+// division, clamped (core::image::channel_reduction,
+// mlx/data/core/image/ImageTransform.cpp:159-180).
+__device__ __forceinline__ unsigned gray_mix(const LaunchParams& p, unsigned r, unsigned g, unsigned b) {
+  int v = ((int)r * p.gray_m[0] + (int)g * p.gray_m[1] + (int)b * p.gray_m[2] + p.gray_bias) / 65536;
+  v = v <= 255 ? v : 255;
+  v = v >= 0 ? v : 0;
+  return (unsigned)v;
+}
+
 // One output pixel's C floats; four-channel pixels go out as one 16-byte store
 // when the destination allows it.
 template <int C>
@@ -455,10 +465,11 @@ __device__ __forceinline__ void start_pass(
 // Geometric-output rows [by, by+nr) (nr <= kTileH) x columns [gx_lo, gx_hi) of
 // a resize sample, sub_w columns per pass, written to the batch tensor.  The
 // copies of pass t+1 are in flight while pass t filters horizontally.
-template <int C>
+template <int C, bool GRAY>
 __device__ void resize_rows(
     const DevSample& s, const LaunchParams& p, const Smem& sm, unsigned& parity, bool& first_use,
     int by, int nr, int gx_lo, int gx_hi) {
+  constexpr int CO = GRAY ? 1 : C;   // channels of the batch tensor
   const int tid = threadIdx.x;
   const Axis ay = make_axis(s.pre_h, s.geom_h);
   const Axis ax = make_axis(s.pre_w, s.geom_w);
@@ -544,7 +555,7 @@ __device__ void resize_rows(
   }
 
   float* base = reinterpret_cast<float*>(s.dst);
-  const size_t row_stride = (size_t)s.slot_w * C;
+  const size_t row_stride = (size_t)s.slot_w * CO;
   const bool vec_ok = (reinterpret_cast<uintptr_t>(base) & 15) == 0;
   int it = 0;
   for (;;) {
@@ -719,24 +730,44 @@ __device__ void resize_rows(
           px = s.post_w - 1 - px;
         }
         const int oy = by + rg * 4 - s.post_y;
-        float* dst = base + ((size_t)oy * s.slot_w + px) * C;
+        float* dst = base + ((size_t)oy * s.slot_w + px) * CO;
         const int left = nr - rg * 4;
-        float out[4][C];
+        float out[4][CO];
+        if (GRAY) {
+          // the resized pixel is quantised first, as the image the reference hands
+          // to its channel reduction is; then the fixed-point mix, then the cast
+          unsigned q[4][C];
 #pragma unroll
-        for (int c = 0; c < C; c++) {
-          float a0, a1, a2, a3;
-          unpack2(acc[c][0], a0, a1);
-          unpack2(acc[c][1], a2, a3);
-          const unsigned lut = sm.lut + (unsigned)c * 1024u;
-          out[0][c] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a0)));
-          out[1][c] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a1)));
-          out[2][c] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a2)));
-          out[3][c] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a3)));
+          for (int c = 0; c < C; c++) {
+            float a0, a1, a2, a3;
+            unpack2(acc[c][0], a0, a1);
+            unpack2(acc[c][1], a2, a3);
+            q[0][c] = quantise_sat(a0);
+            q[1][c] = quantise_sat(a1);
+            q[2][c] = quantise_sat(a2);
+            q[3][c] = quantise_sat(a3);
+          }
+#pragma unroll
+          for (int r = 0; r < 4; r++) {
+            out[r][0] = __uint_as_float(lds_u32<0>(sm.lut + 4u * gray_mix(p, q[r][0], q[r][1 % C], q[r][2 % C])));
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < C; c++) {
+            float a0, a1, a2, a3;
+            unpack2(acc[c][0], a0, a1);
+            unpack2(acc[c][1], a2, a3);
+            const unsigned lut = sm.lut + (unsigned)c * 1024u;
+            out[0][c % CO] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a0)));
+            out[1][c % CO] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a1)));
+            out[2][c % CO] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a2)));
+            out[3][c % CO] = __uint_as_float(lds_u32<0>(lut + 4u * quantise_sat(a3)));
+          }
         }
 #pragma unroll
         for (int r = 0; r < 4; r++) {
           if (r < left) {
-            store_pixel<C>(dst + r * row_stride, out[r], vec_ok);
+            store_pixel<CO>(dst + r * row_stride, out[r], vec_ok);
           }
         }
       }
@@ -776,9 +807,10 @@ __device__ __forceinline__ bool affine_source(
 // of a row.  The cast table is read from shared memory (lut_s); the four pixels
 // leave as 16-byte stores when the row segment allows it.  Without a geometric
 // op the four source pixels are adjacent too and come as aligned words.
-template <int C>
+template <int C, bool GRAY>
 __device__ void gather_rows(
     const DevSample& s, const LaunchParams& p, unsigned lut_s, int y0, int vy1, int xa, int xb) {
+  constexpr int CO = GRAY ? 1 : C;
   const int nvx = xb - xa;
   const int nvy = vy1 - y0;
   const int quads = (nvx + 3) >> 2;
@@ -787,8 +819,8 @@ __device__ void gather_rows(
   const float thh = (float)((double)s.geom_h / 2.0);
   const float wh = (float)((double)s.pre_w / 2.0);
   const float hh = (float)((double)s.pre_h / 2.0);
-  const size_t row_floats = (size_t)s.slot_w * C;
-  const bool vec_ok = (row_floats & 3) == 0 && ((xa * C) & 3) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+  const size_t row_floats = (size_t)s.slot_w * CO;
+  const bool vec_ok = (row_floats & 3) == 0 && ((xa * CO) & 3) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
   // last 4-byte word of the source image: nothing behind it is read
   const uintptr_t last_word = (reinterpret_cast<uintptr_t>(s.src) + (size_t)s.src_h * s.src_w * C - 1) & ~(uintptr_t)3;
   for (int i = threadIdx.x; i < nvy * quads; i += kThreads) {
@@ -859,19 +891,23 @@ __device__ void gather_rows(
         }
       }
     }
-    float out[4][C];
+    float out[4][CO];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
+      if (GRAY) {
+        out[j][0] = __uint_as_float(lds_u32<0>(lut_s + 4u * gray_mix(p, px[j][0], px[j][1 % C], px[j][2 % C])));
+      } else {
 #pragma unroll
-      for (int ch = 0; ch < C; ch++) {
-        out[j][ch] = __uint_as_float(lds_u32<0>(lut_s + (unsigned)ch * 1024u + 4u * px[j][ch]));
+        for (int ch = 0; ch < C; ch++) {
+          out[j][ch % CO] = __uint_as_float(lds_u32<0>(lut_s + (unsigned)ch * 1024u + 4u * px[j][ch]));
+        }
       }
     }
-    float* dst = base + ((size_t)(y0 + ry) * s.slot_w + x_first) * C;
+    float* dst = base + ((size_t)(y0 + ry) * s.slot_w + x_first) * CO;
     if (vec_ok && npx == 4) {
       const float* o = &out[0][0];
 #pragma unroll
-      for (int k = 0; k < C; k++) {
+      for (int k = 0; k < CO; k++) {
         reinterpret_cast<float4*>(dst)[k] = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
       }
     } else {
@@ -879,8 +915,8 @@ __device__ void gather_rows(
       for (int j = 0; j < 4; j++) {
         if (j < npx) {
 #pragma unroll
-          for (int ch = 0; ch < C; ch++) {
-            dst[j * C + ch] = out[j][ch];
+          for (int ch = 0; ch < CO; ch++) {
+            dst[j * CO + ch] = out[j][ch];
           }
         }
       }
@@ -889,7 +925,7 @@ __device__ void gather_rows(
 }
 
 // One CTA: rows [y0, y0 + kTileH) of one slot, columns of p.band_tiles tiles.
-template <int C>
+template <int C, bool GRAY>
 __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
   unsigned t = blockIdx.x;
   const int tb = t % p.bands_x;
@@ -910,19 +946,20 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
   const int vy1 = min(y1, s.post_h);
   const int vx1 = min(x1, s.post_w);
   const bool has_valid = (y0 < vy1) && (x0 < vx1);
+  constexpr int CO = GRAY ? 1 : C;
   float padf[4];
 #pragma unroll
   for (int c = 0; c < 4; c++) {
-    padf[c] = c < C ? __ldg(p.lut + c * 256 + p.pad_px) : 0.0f;
+    padf[c] = c < CO ? __ldg(p.lut + c * 256 + p.pad_px) : 0.0f;
   }
   float* out = reinterpret_cast<float*>(s.dst);
   if (!has_valid) {
-    fill_rect_f32<C>(out, s.slot_w, y0, y1, x0, x1, padf);
+    fill_rect_f32<CO>(out, s.slot_w, y0, y1, x0, x1, padf);
     return;
   }
   Smem sm;
   smem_layout(p, smem_addr(smem_raw), &sm);
-  for (int i = threadIdx.x; i < C * 256; i += kThreads) {
+  for (int i = threadIdx.x; i < CO * 256; i += kThreads) {
     sp<float>(sm.lut)[i] = __ldg(p.lut + i);
   }
   if (s.mode == kModeResize) {
@@ -942,26 +979,33 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
     unsigned parity = 0;
     bool first_use = true;
     for (int by = s.post_y + y0; by < s.post_y + vy1; by += s.sub_h) {
-      resize_rows<C>(s, p, sm, parity, first_use, by, min(s.sub_h, s.post_y + vy1 - by), gx_lo, gx_hi);
+      resize_rows<C, GRAY>(s, p, sm, parity, first_use, by, min(s.sub_h, s.post_y + vy1 - by), gx_lo, gx_hi);
     }
   } else {
     __syncthreads();
-    gather_rows<C>(s, p, sm.lut, y0, vy1, x0, vx1);
+    gather_rows<C, GRAY>(s, p, sm.lut, y0, vy1, x0, vx1);
   }
   // pad the part of the band outside the post window
-  fill_rect_f32<C>(out, s.slot_w, vy1, y1, x0, x1, padf);
-  fill_rect_f32<C>(out, s.slot_w, y0, vy1, vx1, x1, padf);
+  fill_rect_f32<CO>(out, s.slot_w, vy1, y1, x0, x1, padf);
+  fill_rect_f32<CO>(out, s.slot_w, y0, vy1, vx1, x1, padf);
 }
 
 __global__ void __launch_bounds__(kThreads, 3) fused_fast_kernel(const LaunchParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   if (p.c_in == 3) {
-    run_band<3>(p, smem_raw);
+    run_band<3, false>(p, smem_raw);
   } else if (p.c_in == 1) {
-    run_band<1>(p, smem_raw);
+    run_band<1, false>(p, smem_raw);
   } else {
-    run_band<4>(p, smem_raw);
+    run_band<4, false>(p, smem_raw);
   }
+}
+
+// Launches that end in the channel reduction: three channels in, one out.  A
+// kernel of its own, so that the usual one's register allocation is not touched.
+__global__ void __launch_bounds__(kThreads, 3) fused_fast_gray_kernel(const LaunchParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  run_band<3, true>(p, smem_raw);
 }
 
 } // namespace
@@ -990,6 +1034,11 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
     if (e != cudaSuccess) {
       return e;
     }
+    e = cudaFuncSetAttribute(
+        fused_fast_gray_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_layout(worst, 0u, nullptr));
+    if (e != cudaSuccess) {
+      return e;
+    }
     e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) {
       return e;
@@ -1013,7 +1062,11 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
   if (blocks > 0x7fffffffULL) {
     return cudaErrorInvalidConfiguration;
   }
-  fused_fast_kernel<<<(unsigned)blocks, kThreads, fused_fast_smem_bytes(p), stream>>>(p);
+  if (p.gray) {
+    fused_fast_gray_kernel<<<(unsigned)blocks, kThreads, fused_fast_smem_bytes(p), stream>>>(p);
+  } else {
+    fused_fast_kernel<<<(unsigned)blocks, kThreads, fused_fast_smem_bytes(p), stream>>>(p);
+  }
   return cudaGetLastError();
 }
 

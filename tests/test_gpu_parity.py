@@ -309,3 +309,37 @@ def test_float32_resize_cases(pkg, ctx, oracle, case, cast):
     want = _oracle_batches(oracle, samples, ops, 3, cast, 5.0)
     got = _fused_batches(pkg, ctx, oracle, samples, ops, 3, cast, 5.0)
     _compare(got, want, True, cast)
+
+
+# ---------------------------------------------------------------- float32 kernel, channel reduction
+GRAY_CASES = [
+    [("image_resize", dict(key="image", w=61, h=47)),
+     ("image_channel_reduction", dict(key="image", preset="default"))],
+    [("image_random_h_flip", dict(key="image", prob=1.0)),
+     ("image_resize_smallest_side", dict(key="image", size=150)),
+     ("image_center_crop", dict(key="image", w=100, h=90)),
+     ("image_channel_reduction", dict(key="image", preset="rec601"))],
+    [("image_random_crop", dict(key="image", w=70, h=50)),
+     ("image_random_h_flip", dict(key="image", prob=0.5)),
+     ("image_channel_reduction", dict(key="image", preset="rec709"))],
+    [("image_rotate", dict(key="image", angle=-17.0, crop=True)),
+     ("image_channel_reduction", dict(key="image", preset="rec2020"))],
+    [("image_channel_reduction", dict(key="image", preset="green"))],
+]
+
+
+@pytest.mark.parametrize("case", range(len(GRAY_CASES)))
+@pytest.mark.parametrize("cast", [(), "norm"])
+def test_float32_gray_cases(pkg, ctx, oracle, case, cast):
+    """Chains that end in the channel reduction, float32 out: the quantised
+    pixel goes through the fixed-point mix, then the one-channel cast."""
+    ops = GRAY_CASES[case]
+    rng = np.random.default_rng(300 + case)
+    samples = [{"image": rng.integers(0, 256, (97 - 3 * i, 131 - 5 * i, 3), dtype=np.uint8)} for i in range(4)]
+    if cast == "norm":
+        cast = ([0.45], [0.225])
+    has_resize = any(n.startswith("image_resize") for n, _ in ops)
+    want = _oracle_batches(oracle, samples, ops, 4, cast, 2.0)
+    got = _fused_batches(pkg, ctx, oracle, samples, ops, 4, cast, 2.0)
+    assert got[0].shape[-1] == 1
+    _compare(got, want, has_resize, cast)
