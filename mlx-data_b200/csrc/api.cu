@@ -286,6 +286,7 @@ int mlxd_fused_batch_on_stream(
   p.mid_float4s = need.mid_float4s;
   p.weight_floats = need.weight_floats;
   p.u_cap = need.u_cap;
+  p.fast_smem_bytes = (int32_t)need.fast_smem_bytes;
   choose_kernel(p, need);
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)b.slot_h * b.slot_w * p.c_out * esize;

@@ -175,6 +175,14 @@ static int plan_resize(DevSample& s, int C, int i, PassNeed& need, long long pas
         need.mid_float4s = std::max(need.mid_float4s, n.mid_float4s);
         need.weight_floats = std::max(need.weight_floats, n.weight_floats);
         need.u_cap = std::max(need.u_cap, n.u_cap);
+        // the float32 kernel lays a CTA out from its own sample's needs
+        s.need_src = n.src_bytes;
+        s.need_mid4 = n.mid_float4s;
+        s.need_wts_ucap = n.weight_floats | (n.u_cap << 16);
+        need.sum_bytes = std::max<int64_t>(need.sum_bytes, pass_bytes(n));
+        need.fast_smem_bytes = std::max<int64_t>(
+            need.fast_smem_bytes,
+            (int64_t)fused_fast_layout_bytes(C, n.u_cap, n.weight_floats, n.mid_float4s, n.src_bytes));
         return MLXD_OK;
       }
       if (budgeted && sub_h <= 4 && sub_w <= 16) {
@@ -261,14 +269,16 @@ int plan_into(const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b, 
   // full-size passes at two CTAs per SM are the better deal.
   const long long budgets[3] = {kPassBudgetBytes, kPassBudgetBytes - 8 * 1024, kPassBudgetBytes};
   for (int k = 0; k < 3; k++) {
-    need = PassNeed{0, 0, 0, 0, 0};
+    need = PassNeed{0, 0, 0, 0, 0, 0, 0};
     for (int i = 0; i < n; i++) {
       const int rc = plan_one_sample(samples[i], i, b, out[i], need, budgets[k]);
       if (rc != MLXD_OK) {
         return rc;
       }
     }
-    if (pass_bytes(need) <= kPassBudgetBytes) {
+    // the float32 kernel needs the largest per-sample sum, the generic one the sum of the largest parts
+    const bool fast = b->out_dtype == MLXD_F32 && b->channels != 2;
+    if ((fast ? (long long)need.sum_bytes : pass_bytes(need)) <= kPassBudgetBytes) {
       break;
     }
   }
@@ -468,6 +478,7 @@ int enqueue_on_lane(
   p.mid_float4s = need.mid_float4s;
   p.weight_floats = need.weight_floats;
   p.u_cap = need.u_cap;
+  p.fast_smem_bytes = (int32_t)need.fast_smem_bytes;
   choose_kernel(p, need);
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)batch->slot_h * batch->slot_w * p.c_out * esize;

@@ -40,7 +40,11 @@ struct __align__(16) DevSample {
   int32_t cap_y, cap_x;   // resize: tap-count bound per axis
   float mx[6];
   int32_t r0_staged;      // host use: first source row held by the staged copy
-  int32_t pad_[2];
+  // resize, float32 kernel: this sample's own shared-memory needs.  A CTA lays
+  // its shared memory out from these, so a launch is sized by the largest sum
+  // over its samples, not by the sum of the largest parts.
+  int32_t need_src, need_mid4;
+  int32_t need_wts_ucap;  // weight floats in the low 16 bits, u_cap above
 };
 
 struct LaunchParams {
@@ -64,6 +68,7 @@ struct LaunchParams {
   int32_t use_fast;           // 1: the float32 kernel (fused_fast.cu) can run this launch
   int32_t band_tiles;         // float32 kernel: tiles per CTA along a row band (set at launch)
   int32_t bands_x;            // float32 kernel: CTAs per row band
+  int32_t fast_smem_bytes;    // float32 kernel: dynamic shared memory of the launch
 };
 
 // Shared-memory need of one resize pass, from the planner's conservative bounds.
@@ -73,10 +78,16 @@ struct PassNeed {
   int32_t weight_floats;
   int32_t u_cap;
   int32_t needs_generic;      // a sample only the generic kernel handles (none at present)
+  int64_t sum_bytes;          // largest per-sample sum of the parts that grow with the pass (pass_bytes)
+  int64_t fast_smem_bytes;    // float32 kernel: largest per-sample shared-memory layout
 };
 
 // Bytes of dynamic shared memory the kernel needs for these parameters.
 size_t fused_batch_smem_bytes(const LaunchParams& p);
+
+// Dynamic shared memory of the float32 kernel for a sample with these needs
+// (c_out channels in the cast table).
+size_t fused_fast_layout_bytes(int c_out, int u_cap, int weight_floats, int mid_float4s, int src_tile_bytes);
 
 // Launch the float32 kernel when p.use_fast is set, else the generic one.
 cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream);

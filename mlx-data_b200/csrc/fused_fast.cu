@@ -330,11 +330,16 @@ __host__ __device__ inline size_t align16(size_t v) {
 
 // Fills `out` with addresses relative to `base` (the shared-space address of
 // the dynamic shared memory) and returns the bytes needed.
-__host__ __device__ inline size_t smem_layout(const LaunchParams& p, unsigned base, Smem* out) {
+// The parts of it whose size depends on the sample.
+struct Caps {
+  int u_cap, weight_floats, mid_float4s, src_tile_bytes;
+};
+
+__host__ __device__ inline size_t smem_layout(int c_out, const Caps& p, unsigned base, Smem* out) {
   Smem sm;
   size_t off = 0;
   sm.lut = base + (unsigned)off;
-  off += (size_t)p.c_out * 256 * sizeof(float);
+  off += (size_t)c_out * 256 * sizeof(float);
   sm.tab0 = base + (unsigned)off;
   sm.wh_off = (unsigned)align16(kTabUrow + (size_t)8 * p.u_cap * sizeof(int2));
   sm.tab_stride = (unsigned)align16(sm.wh_off + (size_t)p.weight_floats * 2 * sizeof(float));
@@ -404,7 +409,7 @@ __device__ __forceinline__ PassGeom pass_geom(const DevSample& s, const Axis& ax
 // of the vertical unions).
 template <int C>
 __device__ __forceinline__ void start_pass(
-    const DevSample& s, const LaunchParams& p, const Smem& sm, unsigned tab, const PassGeom& g,
+    const DevSample& s, const LaunchParams& p, const Caps& caps, const Smem& sm, unsigned tab, const PassGeom& g,
     const Axis& ax, int nr, int rlo, int rows) {
   const int tid = threadIdx.x;
   const size_t src_pitch = (size_t)s.src_w * C;
@@ -456,7 +461,7 @@ __device__ __forceinline__ void start_pass(
       const int phase = (int)((reinterpret_cast<uintptr_t>(g.g0) + (size_t)sr * src_pitch) & 15);
       // aligned sources: boff is a multiple of 8 and the shift is unused
       const int boff = sr * g.pitch_s + phase - g.common;
-      sp<int2>(tab + kTabUrow)[rp * p.u_cap + e] =
+      sp<int2>(tab + kTabUrow)[rp * caps.u_cap + e] =
           make_int2((int)(sm.srct + (unsigned)(boff & ~3)), (boff & 3) * 8);
     }
   }
@@ -467,7 +472,7 @@ __device__ __forceinline__ void start_pass(
 // copies of pass t+1 are in flight while pass t filters horizontally.
 template <int C, bool GRAY>
 __device__ void resize_rows(
-    const DevSample& s, const LaunchParams& p, const Smem& sm, unsigned& parity, bool& first_use,
+    const DevSample& s, const LaunchParams& p, const Caps& caps, const Smem& sm, unsigned& parity, bool& first_use,
     int by, int nr, int gx_lo, int gx_hi) {
   constexpr int CO = GRAY ? 1 : C;   // channels of the batch tensor
   const int tid = threadIdx.x;
@@ -495,9 +500,9 @@ __device__ void resize_rows(
 
   // ---- vertical union weights of every pair of output rows ------------------------
   const int nrp = (nr + 1) >> 1;
-  for (int i = tid; i < nrp * p.u_cap; i += kThreads) {
-    const int rp = i / p.u_cap;
-    const int e = i - rp * p.u_cap;
+  for (int i = tid; i < nrp * caps.u_cap; i += kThreads) {
+    const int rp = i / caps.u_cap;
+    const int e = i - rp * caps.u_cap;
     const int o0 = by + rp * 2;
     const int on = min(2, nr - rp * 2);
     int lo[2], hi[2];
@@ -510,8 +515,8 @@ __device__ void resize_rows(
     const int u = ufirst + e;
     if (e == 0) {
       int cnt = ulast - ufirst + 1;
-      if (cnt > p.u_cap) {
-        cnt = p.u_cap;
+      if (cnt > caps.u_cap) {
+        cnt = caps.u_cap;
         atomicOr(p.status, 8);
       }
       sp<int>(sm.ucount)[rp] = cnt;
@@ -542,13 +547,13 @@ __device__ void resize_rows(
   __syncthreads();   // ucount is read by start_pass
 
   PassGeom cur = pass_geom<C>(s, ax, rlo, gx_lo, min(s.sub_w, gx_hi - gx_lo));
-  if (rows * cur.pitch_s > p.src_tile_bytes || ngroups * C * plane_slots<C>(cur.ncols) > p.mid_float4s) {
+  if (rows * cur.pitch_s > caps.src_tile_bytes || ngroups * C * plane_slots<C>(cur.ncols) > caps.mid_float4s) {
     if (tid == 0) {
       atomicOr(p.status, 2);
     }
     return;
   }
-  start_pass<C>(s, p, sm, sm.tab0, cur, ax, nr, rlo, rows);
+  start_pass<C>(s, p, caps, sm, sm.tab0, cur, ax, nr, rlo, rows);
   __syncthreads();
   if (tid == 0) {
     mbar_arrive(sm.bar);
@@ -589,9 +594,9 @@ __device__ void resize_rows(
             const int cnt = sp<int>(sm.ucount)[rp];
             f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (cur.shifted) {
-              vertical_taps<true>(urow_base + rp * p.u_cap * 8, uw_base + rp * p.u_cap * 16, 8u * g, cnt, acc);
+              vertical_taps<true>(urow_base + rp * caps.u_cap * 8, uw_base + rp * caps.u_cap * 16, 8u * g, cnt, acc);
             } else {
-              vertical_taps<false>(urow_base + rp * p.u_cap * 8, uw_base + rp * p.u_cap * 16, 8u * g, cnt, acc);
+              vertical_taps<false>(urow_base + rp * caps.u_cap * 8, uw_base + rp * caps.u_cap * 16, 8u * g, cnt, acc);
             }
             // the pair's rows are one half of a float4 of its group of four rows
             const unsigned pb = sm.mid + (unsigned)(rp >> 1) * group_bytes + (unsigned)(rp & 1) * 8u;
@@ -613,9 +618,9 @@ __device__ void resize_rows(
           const int cnt = sp<int>(sm.ucount)[rp];
           f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
           if (cur.shifted) {
-            vertical_taps<true>(urow_base + rp * p.u_cap * 8, uw_base + rp * p.u_cap * 16, 8u * g, cnt, acc);
+            vertical_taps<true>(urow_base + rp * caps.u_cap * 8, uw_base + rp * caps.u_cap * 16, 8u * g, cnt, acc);
           } else {
-            vertical_taps<false>(urow_base + rp * p.u_cap * 8, uw_base + rp * p.u_cap * 16, 8u * g, cnt, acc);
+            vertical_taps<false>(urow_base + rp * caps.u_cap * 8, uw_base + rp * caps.u_cap * 16, 8u * g, cnt, acc);
           }
           const int j0 = 8 * g - cur.common;
           unsigned b[C];
@@ -638,14 +643,14 @@ __device__ void resize_rows(
     PassGeom nxt = cur;
     if (more) {
       nxt = pass_geom<C>(s, ax, rlo, next_bx, min(s.sub_w, gx_hi - next_bx));
-      if (rows * nxt.pitch_s > p.src_tile_bytes || ngroups * C * plane_slots<C>(nxt.ncols) > p.mid_float4s) {
+      if (rows * nxt.pitch_s > caps.src_tile_bytes || ngroups * C * plane_slots<C>(nxt.ncols) > caps.mid_float4s) {
         if (tid == 0) {
           atomicOr(p.status, 2);
         }
         return;
       }
       fence_async_smem();
-      start_pass<C>(s, p, sm, tab_next, nxt, ax, nr, rlo, rows);
+      start_pass<C>(s, p, caps, sm, tab_next, nxt, ax, nr, rlo, rows);
     }
 
     // ---- horizontal filter: thread = (output column, group of four rows), all channels ----
@@ -957,8 +962,14 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
     fill_rect_f32<CO>(out, s.slot_w, y0, y1, x0, x1, padf);
     return;
   }
+  // a resize sample lays the CTA's shared memory out from its own needs
+  Caps caps;
+  caps.u_cap = s.need_wts_ucap >> 16;
+  caps.weight_floats = s.need_wts_ucap & 0xffff;
+  caps.mid_float4s = s.need_mid4;
+  caps.src_tile_bytes = s.need_src;
   Smem sm;
-  smem_layout(p, smem_addr(smem_raw), &sm);
+  smem_layout(p.c_out, caps, smem_addr(smem_raw), &sm);
   for (int i = threadIdx.x; i < CO * 256; i += kThreads) {
     sp<float>(sm.lut)[i] = __ldg(p.lut + i);
   }
@@ -979,7 +990,7 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
     unsigned parity = 0;
     bool first_use = true;
     for (int by = s.post_y + y0; by < s.post_y + vy1; by += s.sub_h) {
-      resize_rows<C, GRAY>(s, p, sm, parity, first_use, by, min(s.sub_h, s.post_y + vy1 - by), gx_lo, gx_hi);
+      resize_rows<C, GRAY>(s, p, caps, sm, parity, first_use, by, min(s.sub_h, s.post_y + vy1 - by), gx_lo, gx_hi);
     }
   } else {
     __syncthreads();
@@ -1010,8 +1021,9 @@ __global__ void __launch_bounds__(kThreads, 3) fused_fast_gray_kernel(const Laun
 
 } // namespace
 
-size_t fused_fast_smem_bytes(const LaunchParams& p) {
-  return smem_layout(p, 0u, nullptr);   // without a resize in the launch only the cast table
+size_t fused_fast_layout_bytes(int c_out, int u_cap, int weight_floats, int mid_float4s, int src_tile_bytes) {
+  const Caps caps{u_cap, weight_floats, mid_float4s, src_tile_bytes};
+  return smem_layout(c_out, caps, 0u, nullptr);   // without a resize only the cast table
 }
 
 cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
@@ -1023,19 +1035,12 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
     return e;
   }
   if (configured_device != dev) {
-    LaunchParams worst = p_in;
-    worst.c_out = 4;
-    worst.weight_floats = kWeightFloats;
-    worst.mid_float4s = kMidFloats / 4;
-    worst.src_tile_bytes = kSrcTileBytes;
-    worst.u_cap = kMaxStagedRows;
-    e = cudaFuncSetAttribute(
-        fused_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_layout(worst, 0u, nullptr));
+    const int most = (int)fused_fast_layout_bytes(4, kMaxStagedRows, kWeightFloats, kMidFloats / 4, kSrcTileBytes);
+    e = cudaFuncSetAttribute(fused_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e != cudaSuccess) {
       return e;
     }
-    e = cudaFuncSetAttribute(
-        fused_fast_gray_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_layout(worst, 0u, nullptr));
+    e = cudaFuncSetAttribute(fused_fast_gray_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e != cudaSuccess) {
       return e;
     }
@@ -1062,10 +1067,12 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
   if (blocks > 0x7fffffffULL) {
     return cudaErrorInvalidConfiguration;
   }
+  // sized by the planner: the largest layout any one sample of the launch needs
+  const size_t smem = p.fast_smem_bytes > 0 ? (size_t)p.fast_smem_bytes : fused_fast_layout_bytes(p.c_out, 0, 0, 0, 0);
   if (p.gray) {
-    fused_fast_gray_kernel<<<(unsigned)blocks, kThreads, fused_fast_smem_bytes(p), stream>>>(p);
+    fused_fast_gray_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
   } else {
-    fused_fast_kernel<<<(unsigned)blocks, kThreads, fused_fast_smem_bytes(p), stream>>>(p);
+    fused_fast_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
   }
   return cudaGetLastError();
 }
