@@ -12,6 +12,7 @@
 #include "mlx/data/Array.h"
 #include "mlx/data/Sample.h"
 #include "mlx/data/op/ImageTransform.h"
+#include "mlx/data/op/LoadImage.h"
 #include "mlx/data/op/Pad.h"
 #include "mlx/data/op/Slice.h"
 #include "mlx/data/op/KeyTransform.h"
@@ -138,6 +139,15 @@ class Dataset {
   T random_slice_if(bool cond, const std::string& ikey, std::vector<int> dims, std::vector<int64_t> sizes,
                     const std::string& okey = "") const {
     MLXD_IF_TWIN(random_slice, ikey, std::move(dims), std::move(sizes), okey);
+  }
+
+  T load_image(const std::string& ikey, const std::string& prefix = "", bool info = false,
+               const std::string& format = "RGB", bool from_memory = false, const std::string& okey = "") const {
+    return add_(std::make_shared<op::LoadImage>(ikey, prefix, info, format, from_memory, okey));
+  }
+  T load_image_if(bool cond, const std::string& ikey, const std::string& prefix = "", bool info = false,
+                  const std::string& format = "RGB", bool from_memory = false, const std::string& okey = "") const {
+    MLXD_IF_TWIN(load_image, ikey, prefix, info, format, from_memory, okey);
   }
 
   T key_transform(const std::string& ikey, op::KeyTransform::Fn fn, const std::string& okey = "") const {

@@ -286,6 +286,13 @@ void bind_ops(PyClass& c) {
           return self.pad_to_size_if(cond, key, dim, sizes, pad_value, okey);
         },
         py::arg("cond"), py::arg("key"), py::arg("dim"), py::arg("size"), py::arg("pad_value"), py::arg(okd) = "");
+  c.def("load_image", &T::load_image, nogil(), py::arg("key"), py::arg("prefix") = "", py::arg("info") = false,
+        py::arg("format") = "RGB", py::arg("from_memory") = false, py::arg(okd) = "",
+        "Load the image file named by the array at ``key`` (or, with ``from_memory``, held in it) as uint8 "
+        "[H, W, C], or with ``info`` its (width, height).  This build decodes binary PNM (P5, P6) only; the "
+        "pixels land in page-locked memory that the GPU reads directly.");
+  c.def("load_image_if", &T::load_image_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("prefix") = "",
+        py::arg("info") = false, py::arg("format") = "RGB", py::arg("from_memory") = false, py::arg(okd) = "");
   c.def("image_center_crop", &T::image_center_crop, nogil(), py::arg("key"), py::arg("w"), py::arg("h"),
         py::arg(okd) = "", "Center crop the image at ``key`` to ``w`` x ``h``.");
   c.def("image_center_crop_if", &T::image_center_crop_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("w"),

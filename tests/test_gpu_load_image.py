@@ -1,0 +1,55 @@
+"""load_image feeding the fused path: binary PNM files (and in-memory copies)
+are read into page-locked memory, then resized, cropped, batched and cast in
+one launch per batch; the result must equal the oracle's on the pixel arrays
+the files were written from."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+OPS = [("image_resize_smallest_side", dict(key="image", size=40)),
+       ("image_center_crop", dict(key="image", w=36, h=32)),
+       ("image_random_h_flip", dict(key="image", prob=0.5))]
+
+
+def _write(path, arr):
+    h, w = arr.shape[:2]
+    magic = b"P6" if arr.shape[2] == 3 else b"P5"
+    path.write_bytes(magic + b"\n# c\n%d %d\n255\n" % (w, h) + arr.tobytes())
+
+
+@pytest.mark.parametrize("channels", [3, 1])
+@pytest.mark.parametrize("from_memory", [False, True])
+def test_load_then_fused_chain(pkg, oracle, tmp_path, channels, from_memory):
+    rng = np.random.default_rng(5 + channels)
+    arrays = [rng.integers(0, 256, (int(rng.integers(50, 90)), int(rng.integers(50, 90)), channels), dtype=np.uint8)
+              for _ in range(6)]
+    samples = []
+    for i, a in enumerate(arrays):
+        name = "im%d.%s" % (i, "ppm" if channels == 3 else "pgm")
+        _write(tmp_path / name, a)
+        if from_memory:
+            samples.append({"image": np.frombuffer((tmp_path / name).read_bytes(), dtype=np.uint8)})
+        else:
+            samples.append({"image": name.encode()})
+    pkg.core.set_state(11)
+    ds = pkg.buffer_from_vector(samples).to_stream().load_image("image", prefix=str(tmp_path), from_memory=from_memory)
+    loaded = [np.asarray(s["image"]) for s in ds]
+    for got, want in zip(loaded, arrays):
+        assert got.dtype == np.uint8 and got.shape == want.shape and np.array_equal(got, want)
+    ds = pkg.buffer_from_vector(samples).to_stream().load_image("image", prefix=str(tmp_path), from_memory=from_memory)
+    for name, kw in OPS:
+        ds = getattr(ds, name)(**kw)
+    before = pkg.core.stats()["kernel_launches"]
+    pkg.core.set_state(11)
+    got = [np.asarray(b["image"]) for b in ds.batch(3).key_cast("image")]
+    launches = pkg.core.stats()["kernel_launches"] - before
+    oracle.set_state(11)
+    want = [b["image"] for b in oracle.run_chain([{"image": a} for a in arrays], OPS, 3, {"image": 0.0}, {"image": None})]
+    assert len(got) == len(want) == 2
+    for g, w in zip(got, want):
+        assert g.shape == w.shape and g.dtype == np.float32
+        d = np.abs(g.astype(np.float64) - w.astype(np.float64))
+        assert d.max() <= 1.0001 / 255 and (d > 0).mean() <= 1e-3
+    # page-locked sources: one gather launch and one fused launch per batch
+    assert launches == 2 * len(want)
