@@ -104,6 +104,12 @@ __device__ __forceinline__ float pad_pick(const float (&padf)[4], int m) {
 
 // Pad value (already cast) into the rectangle [ya, yb) x [xa, xb) of a slot
 // with CO channels, 16-byte stores wherever the row segment allows.
+//
+// When the row pitch is a multiple of 16 bytes every row of the rectangle
+// starts at the same offset within a 16-byte unit, so a thread works out its
+// column position and its four values once and walks down the rows with
+// nothing but stores; the CTA's threads are dealt over (column position, row
+// phase) so that narrow rectangles still use all of them.
 template <int CO>
 __device__ __forceinline__ void fill_rect_f32(
     float* base, int slot_w, int ya, int yb, int xa, int xb, const float (&padf)[4]) {
@@ -111,12 +117,48 @@ __device__ __forceinline__ void fill_rect_f32(
     return;
   }
   const int L = (xb - xa) * CO;
-  const int Q = ((L + 3) >> 2) + 2;
   const int ny = yb - ya;
+  const size_t row_floats = (size_t)slot_w * CO;
+  float* row0 = base + ((size_t)ya * slot_w + xa) * CO;
+  if ((row_floats & 3) == 0) {
+    const int mis = (int)((reinterpret_cast<uintptr_t>(row0) >> 2) & 3);
+    int head = (4 - mis) & 3;
+    head = head > L ? L : head;
+    const int nvec = (L - head) >> 2;
+    if (nvec > 0) {
+      const int lanes_q = nvec >= kThreads ? kThreads : nvec;
+      const int phases = kThreads / lanes_q;
+      const int r0 = (int)threadIdx.x / lanes_q;
+      if (r0 < phases) {
+        for (int q = (int)threadIdx.x - r0 * lanes_q; q < nvec; q += lanes_q) {
+          const int j = head + 4 * q;
+          const int m = j % CO;
+          const float4 v = make_float4(
+              pad_pick<CO>(padf, m), pad_pick<CO>(padf, (m + 1) % CO), pad_pick<CO>(padf, (m + 2) % CO),
+              pad_pick<CO>(padf, (m + 3) % CO));
+          float* p = row0 + (size_t)r0 * row_floats + j;
+          for (int ry = r0; ry < ny; ry += phases, p += (size_t)phases * row_floats) {
+            *reinterpret_cast<float4*>(p) = v;
+          }
+        }
+      }
+    }
+    // the few floats before the first and after the last aligned unit of each row
+    const int tail = head + 4 * nvec;
+    const int loose = head + (L - tail);
+    for (int i = threadIdx.x; i < ny * loose; i += kThreads) {
+      const int ry = i / loose;
+      const int k = i - ry * loose;
+      const int j = k < head ? k : tail + (k - head);
+      row0[(size_t)ry * row_floats + j] = pad_pick<CO>(padf, j % CO);
+    }
+    return;
+  }
+  const int Q = ((L + 3) >> 2) + 2;
   for (int i = threadIdx.x; i < ny * Q; i += kThreads) {
     const int ry = i / Q;
     const int q = i - ry * Q;
-    float* rowp = base + ((size_t)(ya + ry) * slot_w + xa) * CO;
+    float* rowp = row0 + (size_t)ry * row_floats;
     const int mis = (int)((reinterpret_cast<uintptr_t>(rowp) >> 2) & 3);
     int head = (4 - mis) & 3;
     head = head > L ? L : head;
