@@ -287,7 +287,7 @@ int mlxd_fused_batch_on_stream(
   p.weight_floats = need.weight_floats;
   p.u_cap = need.u_cap;
   p.fast_smem_bytes = (int32_t)need.fast_smem_bytes;
-  choose_kernel(p, need);
+  choose_kernel(p, need, dev.data(), n);
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)b.slot_h * b.slot_w * p.c_out * esize;
   uint64_t algo_src = 0;

@@ -479,7 +479,7 @@ int enqueue_on_lane(
   p.weight_floats = need.weight_floats;
   p.u_cap = need.u_cap;
   p.fast_smem_bytes = (int32_t)need.fast_smem_bytes;
-  choose_kernel(p, need);
+  choose_kernel(p, need, dev.data(), n);
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)batch->slot_h * batch->slot_w * p.c_out * esize;
   const size_t out_bytes = slot_bytes * n;

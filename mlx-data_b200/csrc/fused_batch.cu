@@ -451,9 +451,24 @@ cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-void choose_kernel(LaunchParams& p, const PassNeed& need) {
+void choose_kernel(LaunchParams& p, const PassNeed& need, const DevSample* host_samples, int n) {
   const bool channels_ok = p.c_in == 1 || p.c_in == 3 || p.c_in == 4;
   p.use_fast = (p.out_f32 && channels_ok && !need.needs_generic) ? 1 : 0;
+  // The rows below a sample's post window are one contiguous run of its slot;
+  // when those runs are at least an eighth of the batch they get a linear fill
+  // of their own (pad_fill_kernel), which writes at memory speed.
+  p.pad_apart = 0;
+  if (p.use_fast && n > 0) {
+    unsigned long long rows = 0, below = 0;
+    for (int i = 0; i < n; i++) {
+      const int h = host_samples[i].slot_h;
+      const int ph = host_samples[i].post_h < h ? host_samples[i].post_h : h;
+      const int first = ((ph + kTileH - 1) / kTileH) * kTileH;
+      rows += (unsigned long long)h;
+      below += (unsigned long long)(first < h ? h - first : 0);
+    }
+    p.pad_apart = below * 8 >= rows ? 1 : 0;
+  }
 }
 
 AxisPlan plan_axis(int32_t n_src, int32_t n_dst, int32_t sub) {

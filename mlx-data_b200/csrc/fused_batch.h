@@ -69,6 +69,7 @@ struct LaunchParams {
   int32_t band_tiles;         // float32 kernel: tiles per CTA along a row band (set at launch)
   int32_t bands_x;            // float32 kernel: CTAs per row band
   int32_t fast_smem_bytes;    // float32 kernel: dynamic shared memory of the launch
+  int32_t pad_apart;          // float32 kernel: the padding is written by pad_fill_kernel, launched just before
 };
 
 // Shared-memory need of one resize pass, from the planner's conservative bounds.
@@ -93,8 +94,10 @@ size_t fused_fast_layout_bytes(int c_out, int u_cap, int weight_floats, int mid_
 cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream);
 cudaError_t launch_fused_fast(const LaunchParams& p, cudaStream_t stream);
 
-// Decide which kernel runs a launch; call after the planner filled `need`.
-void choose_kernel(LaunchParams& p, const PassNeed& need);
+// Decide which kernel runs a launch, and whether a ragged batch's padding gets
+// a launch of its own; call after the planner filled `need` and the host copy
+// of the sample table.
+void choose_kernel(LaunchParams& p, const PassNeed& need, const DevSample* host_samples, int n);
 
 // Conservative per-axis bounds used by the host planner.
 struct AxisPlan {

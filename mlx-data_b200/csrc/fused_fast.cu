@@ -959,7 +959,10 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
   }
   float* out = reinterpret_cast<float*>(s.dst);
   if (!has_valid) {
-    fill_rect_f32<CO>(out, s.slot_w, y0, y1, x0, x1, padf);
+    // bands below the post window are pad_fill_kernel's when it runs
+    if (!(p.pad_apart && y0 >= s.post_h)) {
+      fill_rect_f32<CO>(out, s.slot_w, y0, y1, x0, x1, padf);
+    }
     return;
   }
   // a resize sample lays the CTA's shared memory out from its own needs
@@ -1009,6 +1012,71 @@ __global__ void __launch_bounds__(kThreads, 3) fused_fast_kernel(const LaunchPar
     run_band<1, false>(p, smem_raw);
   } else {
     run_band<4, false>(p, smem_raw);
+  }
+}
+
+// The padding below a sample of a ragged batch.  Rows of a slot are contiguous,
+// so everything from the first row band that holds no row of the sample's post
+// window down to the end of the slot is one contiguous run of floats: written
+// here as a linear fill (16-byte stores, consecutive threads on consecutive
+// addresses, kPadChunks CTAs per sample), which runs at memory speed - the
+// band kernels above, writing 16-row strips, reach about 60 % of that.  The
+// strips to the right of the post window stay with the band kernels.
+constexpr int kPadChunks = 128;
+
+template <int CO>
+__device__ __forceinline__ void pad_below(const LaunchParams& p) {
+  const int n = blockIdx.x / kPadChunks;
+  const int chunk = blockIdx.x - n * kPadChunks;
+  if (n >= p.n) {
+    return;
+  }
+  const DevSample* s = p.samples + n;
+  const int slot_h = s->slot_h, slot_w = s->slot_w;
+  const int post_h = s->post_h < slot_h ? s->post_h : slot_h;
+  const int first_row = ((post_h + kTileH - 1) / kTileH) * kTileH;   // first row of the first band without a valid row
+  if (first_row >= slot_h) {
+    return;
+  }
+  float padf[4];
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    padf[c] = c < CO ? __ldg(p.lut + c * 256 + p.pad_px) : 0.0f;
+  }
+  const size_t row_floats = (size_t)slot_w * CO;
+  float* run = reinterpret_cast<float*>(s->dst) + (size_t)first_row * row_floats;   // starts on a pixel: channel 0
+  const size_t len = (size_t)(slot_h - first_row) * row_floats;
+  const size_t mis = (reinterpret_cast<uintptr_t>(run) >> 2) & 3;
+  size_t head = (4 - mis) & 3;
+  head = head > len ? len : head;
+  const size_t nvec = (len - head) >> 2;
+  // this CTA's share of the aligned units
+  const size_t q0 = nvec * (size_t)chunk / kPadChunks;
+  const size_t q1 = nvec * (size_t)(chunk + 1) / kPadChunks;
+  for (size_t q = q0 + threadIdx.x; q < q1; q += kThreads) {
+    const size_t j = head + 4 * q;
+    const int m = (int)(j % CO);
+    *reinterpret_cast<float4*>(run + j) = make_float4(
+        pad_pick<CO>(padf, m), pad_pick<CO>(padf, (m + 1) % CO), pad_pick<CO>(padf, (m + 2) % CO),
+        pad_pick<CO>(padf, (m + 3) % CO));
+  }
+  if (chunk == 0) {
+    // the floats before the first and after the last aligned unit
+    const size_t tail = head + 4 * nvec;
+    for (size_t k = threadIdx.x; k < head + (len - tail); k += kThreads) {
+      const size_t j = k < head ? k : tail + (k - head);
+      run[j] = pad_pick<CO>(padf, (int)(j % CO));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 6) pad_fill_kernel(const LaunchParams p) {
+  if (p.c_out == 3) {
+    pad_below<3>(p);
+  } else if (p.c_out == 1) {
+    pad_below<1>(p);
+  } else {
+    pad_below<4>(p);
   }
 }
 
@@ -1069,6 +1137,13 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
   }
   // sized by the planner: the largest layout any one sample of the launch needs
   const size_t smem = p.fast_smem_bytes > 0 ? (size_t)p.fast_smem_bytes : fused_fast_layout_bytes(p.c_out, 0, 0, 0, 0);
+  if (p.pad_apart) {
+    pad_fill_kernel<<<(unsigned)p.n * kPadChunks, kThreads, 0, stream>>>(p);
+    const cudaError_t pe = cudaGetLastError();
+    if (pe != cudaSuccess) {
+      return pe;
+    }
+  }
   if (p.gray) {
     fused_fast_gray_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
   } else {

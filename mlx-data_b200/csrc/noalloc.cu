@@ -137,7 +137,7 @@ extern "C" int mlxd_fused_batch_noalloc(
   p.weight_floats = need.weight_floats;
   p.u_cap = need.u_cap;
   p.fast_smem_bytes = (int32_t)need.fast_smem_bytes;
-  choose_kernel(p, need);
+  choose_kernel(p, need, table, n);
 
   // The scratch keeps whatever the previous call left.  Its status word is
   // read back first (the kernel of the previous call is ahead of this copy on
