@@ -407,12 +407,17 @@ std::shared_ptr<Buffer> dynamic_batch(
   if (size_source && size_source->size() != n) {
     throw std::runtime_error("DynamicBatch: buffer and reference size buffer do not match in size");
   }
+  // the image ops on top of the source: sized symbolically here, fused into the batches below
+  std::vector<std::shared_ptr<op::FusableOp>> ops;
+  const std::shared_ptr<Buffer> base = peel_image_ops(source, ops);
   std::vector<std::vector<int64_t>> shapes(n);
   for (int64_t i = 0; i < n; i++) {
     if (size_source) {
       auto arr = sample::check_key(size_source->get(i), key, ArrayType::Int64);
       const int64_t* v = arr->data<int64_t>();
       shapes[i].assign(v, v + arr->size());
+    } else if (!ops.empty()) {
+      shapes[i] = core::folded_shape(ops, base->get(i), key);
     } else {
       shapes[i] = sample::check_key(source->get(i), key, ArrayType::Any)->shape();
     }
@@ -425,8 +430,7 @@ std::shared_ptr<Buffer> dynamic_batch(
     *skipped = g.skipped;
   }
   // keep the image ops on top of the permutation, where Batch can fuse them
-  std::vector<std::shared_ptr<op::FusableOp>> ops;
-  std::shared_ptr<Buffer> top = std::make_shared<Perm>(peel_image_ops(source, ops), g.order);
+  std::shared_ptr<Buffer> top = std::make_shared<Perm>(base, g.order);
   if (!ops.empty()) {
     std::vector<std::shared_ptr<op::Op>> generic(ops.begin(), ops.end());
     top = std::make_shared<Transform>(top, generic);

@@ -172,6 +172,26 @@ Sample Batcher::run(const std::vector<Sample>& raw) const {
   return out;
 }
 
+std::vector<int64_t> folded_shape(
+    const std::vector<std::shared_ptr<op::FusableOp>>& ops, const Sample& raw, const std::string& key) {
+  LazySample lazy;
+  for (auto& kv : raw) {
+    lazy[kv.first].array = kv.second;
+  }
+  for (auto& op : ops) {
+    run_op(lazy, *op);
+  }
+  auto it = lazy.find(key);
+  if (it == lazy.end()) {
+    throw std::runtime_error("key <" + key + "> expected");
+  }
+  if (it->second.lazy) {
+    const auto& im = *it->second.lazy;
+    return {im.height(), im.width(), im.channels()};
+  }
+  return it->second.array->shape();
+}
+
 Sample merge_batch(
     const std::vector<Sample>& samples,
     const std::unordered_map<std::string, double>& pad_values,

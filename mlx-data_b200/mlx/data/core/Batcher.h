@@ -53,6 +53,13 @@ class Batcher {
   gpu::Placement placement_;   // the process-wide defaults at the time the node was built
 };
 
+// Shape the array at `key` has after `ops` ran on `raw`, without computing
+// pixels where the ops fold into an image program (random parameters are drawn
+// from core::State exactly as when the ops run for real).  Size-aware batching
+// sizes its samples with this instead of one GPU launch per sample.
+std::vector<int64_t> folded_shape(
+    const std::vector<std::shared_ptr<op::FusableOp>>& ops, const Sample& raw, const std::string& key);
+
 } // namespace core
 } // namespace data
 } // namespace mlx

@@ -69,6 +69,7 @@ class ImageRandomCrop : public ImageTransformOp {
   ImageRandomCrop(const std::string& ikey, int64_t w, int64_t h, const std::string& okey = "")
       : ImageTransformOp(ikey, okey), w_(w), h_(h) {}
   bool fold(gpu::LazyImage& image) const override;
+  bool draws() const override { return true; }
 
  private:
   int64_t w_, h_;
@@ -80,6 +81,7 @@ class ImageRandomAreaCrop : public ImageTransformOp {
       const std::string& ikey, std::pair<float, float> area_range, std::pair<float, float> aspect_ratio_range,
       int num_trial = 10, const std::string& okey = "");
   bool fold(gpu::LazyImage& image) const override;
+  bool draws() const override { return true; }
 
   struct Rect {
     int64_t tx, ty, tw, th;
@@ -98,6 +100,7 @@ class ImageRandomHFlip : public ImageTransformOp {
   ImageRandomHFlip(const std::string& ikey, float prob, const std::string& okey = "")
       : ImageTransformOp(ikey, okey), prob_(prob) {}
   bool fold(gpu::LazyImage& image) const override;
+  bool draws() const override { return true; }
 
  private:
   float prob_;

@@ -52,6 +52,9 @@ class FusableOp : public KeyTransformOp {
   // pixels first.  The batch node checks this before it lets an op draw random
   // parameters, so nothing is drawn twice.
   virtual bool extends_only() const { return false; }
+  // True for ops that draw random parameters: running them twice on a sample
+  // gives two different results.
+  virtual bool draws() const { return false; }
 };
 
 // Arbitrary host callback on one key (this is how Python lambdas enter a pipeline).

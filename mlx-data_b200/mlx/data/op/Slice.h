@@ -115,6 +115,8 @@ class RandomSlice : public FusableOp {
     return image.crop(off[1], off[0], len[1], len[0]);
   }
 
+  bool draws() const override { return true; }
+
  private:
   std::vector<int> dims_;
   std::vector<int64_t> sizes_;

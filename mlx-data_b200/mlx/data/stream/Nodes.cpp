@@ -307,6 +307,16 @@ DynamicBatch::DynamicBatch(
   if (buffer_size <= 0) {
     throw std::runtime_error("DynamicBatch: buffer size must be positive");
   }
+  std::vector<std::shared_ptr<op::FusableOp>> ops;
+  auto below = peel_image_ops(source, ops);
+  bool any_draws = false;
+  for (auto& o : ops) {
+    any_draws = any_draws || o->draws();
+  }
+  if (!ops.empty() && !any_draws) {
+    source_ = below;
+    absorbed_.assign(ops.begin(), ops.end());
+  }
 }
 
 DynamicBatch::~DynamicBatch() {
@@ -343,7 +353,10 @@ std::shared_ptr<buffer::Buffer> DynamicBatch::make_round() const {
   samples.insert(samples.end(), left_out_.begin(), left_out_.end());
   left_out_.clear();
 
-  auto pulled = std::make_shared<buffer::FromVector>(samples);
+  std::shared_ptr<buffer::Buffer> pulled = std::make_shared<buffer::FromVector>(samples);
+  if (!absorbed_.empty()) {
+    pulled = std::make_shared<buffer::Transform>(pulled, absorbed_);
+  }
   std::vector<int64_t> skipped;
   std::shared_ptr<buffer::Buffer> batches = buffer::dynamic_batch(
       pulled, nullptr, key_, min_data_size_, max_data_size_, pad_values_, batch_dims_, drop_outliers_, &skipped);

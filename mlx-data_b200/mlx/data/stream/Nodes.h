@@ -143,10 +143,12 @@ class Repeat : public Stream {
 // positive) get another chance in the next round.  The stream ends with the
 // first round that yields no batch.  The next round is prepared on a worker
 // thread while the current one is handed out; its samples are pulled by
-// num_thread workers.  Samples are taken as the source delivers them - ops
-// above the source have run by then - so the sizes that drive the grouping
-// are the sizes that get batched; padding and stacking of image keys still
-// run as one GPU launch per batch.
+// num_thread workers.  A run of fusable ops directly under this node that draw
+// nothing at random is absorbed: raw samples are pulled, sized symbolically and
+// the ops run fused with each batch.  With an op that draws (random crop, flip,
+// slice) samples are taken as the source delivers them - the ops have run by
+// then, so the sizes that drive the grouping are the sizes that get batched -
+// and padding and stacking of image keys still run as one launch per batch.
 class DynamicBatch : public Stream {
  public:
   DynamicBatch(
@@ -162,7 +164,8 @@ class DynamicBatch : public Stream {
   std::shared_ptr<buffer::Buffer> make_round() const;
   std::future<std::shared_ptr<buffer::Buffer>> start_round() const;
 
-  std::shared_ptr<Stream> source_;
+  std::shared_ptr<Stream> source_;                       // what samples are pulled from
+  std::vector<std::shared_ptr<op::Op>> absorbed_;        // deterministic fusable ops re-applied above each round
   int64_t buffer_size_;
   std::string key_;
   int64_t min_data_size_, max_data_size_;

@@ -158,6 +158,49 @@ def test_four_channel_resize_is_refused_until_accepted(pkg, oracle):
         pkg.core.set_rgba_resize_independent(False)
 
 
+def test_stream_dynamic_batch_of_images(pkg):
+    """The stream variant on ragged images under deterministic ops (absorbed: sized
+    symbolically, fused with each batch) and under a random op (samples taken as
+    the source delivers them): same batches as the reference either way."""
+    ref = refpipe.reference_module()
+    if ref is None:
+        pytest.skip("needs the reference compiled under oracle/_ref")
+    rng = np.random.default_rng(9)
+    samples = []
+    for i in range(37):
+        h, w = int(rng.integers(20, 140)), int(rng.integers(20, 140))
+        samples.append({"image": rng.integers(0, 256, (h, w, 3), dtype=np.uint8), "id": np.int64(i)})
+
+    def chain(dx, random_op):
+        ds = dx.buffer_from_vector(samples).to_stream()
+        if random_op:
+            ds = ds.image_random_crop("image", 20, 20)
+        ds = ds.image_resize_smallest_side("image", 32).slice("image", 0, 0, 48)
+        return ds.dynamic_batch(16, "image", max_data_size=5 * 32 * 64 * 3, pad={"image": 3.0})
+
+    for random_op in (False, True):
+        ref.core.set_state(4)
+        want = [dict(b) for b in chain(ref, random_op)]
+        pkg.core.set_state(4)
+        before = pkg.core.stats()["kernel_launches"]
+        got = [dict(b) for b in chain(pkg, random_op)]
+        used = pkg.core.stats()["kernel_launches"] - before
+        assert len(got) == len(want) and len(want) > 2
+        for g, w in zip(got, want):
+            assert np.array_equal(np.asarray(g["id"]), np.asarray(w["id"]))
+            a, b = np.asarray(g["image"]), np.asarray(w["image"])
+            assert a.shape == b.shape and a.dtype == b.dtype
+            if not random_op:
+                # (with the random crop the pixels depend on which worker thread of the pulling
+                # pool drew the offsets - in the reference too - so only grouping and shapes compare)
+                d = np.abs(a.astype(np.int32) - b.astype(np.int32))
+                assert d.max() <= 1 and (d > 0).mean() <= RESIZE_MISMATCH_MAX
+        if not random_op:
+            # sources are ordinary host arrays: one launch per batch (two extra per batch when
+            # page-locked sources are gathered by a kernel, which these are not)
+            assert used == len(want)
+
+
 CLIP_CHAINS = {
     "resize_crop_flip": [("image_resize_smallest_side", dict(key="image", size=48)),
                          ("image_random_crop", dict(key="image", w=40, h=36)),
@@ -237,8 +280,12 @@ def test_dynamic_batch_of_images(pkg):
                 .dynamic_batch("image", max_data_size=6 * 32 * 64 * 3, pad={"image": 3.0}))
 
     want = [dict(b) for b in chain(ref)]
+    before = pkg.core.stats()["kernel_launches"]
     got_buf = chain(pkg).key_cast("image")
+    # the samples were sized from their recorded programs: no launch so far
+    assert pkg.core.stats()["kernel_launches"] == before
     got = [dict(got_buf[i]) for i in range(len(got_buf))]
+    assert pkg.core.stats()["kernel_launches"] == before + len(got)    # one fused launch per batch
     assert len(got) == len(want)
     for g, w in zip(got, want):
         assert np.array_equal(np.asarray(g["id"]), np.asarray(w["id"]))
