@@ -425,6 +425,11 @@ int prepare_launch(
   p.out_f32 = b->out_dtype == MLXD_F32;
   p.pad_px = (int32_t)(uint8_t)(int32_t)b->pad_value;
   p.status = ctx->d_status;   // callers point this at their lane's word
+  // Test hook (MLXD_TEST_STARVE_WAIT=1, read per launch): the resize bands'
+  // first bounded wait runs out, so the path from the kernel's status word to
+  // the caller's error code can be exercised without a fault or a hang.
+  const char* starve = std::getenv("MLXD_TEST_STARVE_WAIT");
+  p.starve_wait = (starve && starve[0] == '1') ? 1 : 0;
   if (p.out_f32) {
     if (!(b->divisor != 0.0f)) {
       return fail(MLXD_ERR_INVALID, "cast divisor must be non-zero");

@@ -69,7 +69,8 @@ struct LaunchParams {
   int32_t band_tiles;         // float32 kernel: tiles per CTA along a row band (set at launch)
   int32_t bands_x;            // float32 kernel: CTAs per row band
   int32_t fast_smem_bytes;    // float32 kernel: dynamic shared memory of the launch
-  int32_t pad_apart;          // float32 kernel: the padding is written by pad_fill_kernel, launched just before
+  int32_t pad_apart;          // float32 kernel: the rows below each post window are written by pad_fill_kernel
+  int32_t starve_wait;        // test hook: the first pass of every band expects 16 bytes that no copy delivers
 };
 
 // Shared-memory need of one resize pass, from the planner's conservative bounds.

@@ -23,7 +23,10 @@
 namespace mlxd {
 namespace {
 
-constexpr unsigned kSpinLimit = 1u << 22;
+// Polls of an mbarrier before a wait gives up: about a second (a poll that finds
+// the phase incomplete returns after a few microseconds), five orders of
+// magnitude above what a pass's copies take.
+constexpr unsigned kSpinLimit = 1u << 18;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -554,6 +557,9 @@ __device__ void resize_rows(
     return;
   }
   start_pass<C>(s, p, caps, sm, sm.tab0, cur, ax, nr, rlo, rows);
+  if (p.starve_wait && tid == 0) {
+    mbar_expect_tx(sm.bar, 16);   // test hook: bytes that never arrive, the wait below runs out
+  }
   __syncthreads();
   if (tid == 0) {
     mbar_arrive(sm.bar);
