@@ -419,8 +419,12 @@ Placement Runtime::placement() const {
 bool Runtime::pool_take(Pool& pool, size_t bytes, size_t& held, Block& out) {
   std::lock_guard<std::mutex> g(mu_);
   auto it = pool.blocks.lower_bound(bytes);
-  // reuse a block that is at most 25% larger than asked for
-  if (it != pool.blocks.end() && it->first <= bytes + bytes / 4) {
+  // Reuse the smallest free block that is large enough: at most 25 % larger
+  // than asked for - or up to four times for requests of 64 MiB and more,
+  // where a new allocation (and the release of an old one) costs milliseconds
+  // and the batches of one pipeline differ in size by such factors.
+  const size_t slack = bytes >= (size_t(64) << 20) ? 3 * bytes : bytes / 4;
+  if (it != pool.blocks.end() && it->first <= bytes + slack) {
     out = it->second;
     held = it->first;
     pool.bytes -= it->first;
