@@ -252,6 +252,24 @@ void bind_ops(PyClass& c) {
         },
         py::arg("ikey"), py::arg("dims"), py::arg("sizes"), py::arg(okd) = "",
         "Keep a window of ``sizes`` along ``dims`` at a uniformly random offset.");
+  c.def("slice_if",
+        [ints](const T& self, bool cond, const std::string& ikey, py::object dims, py::object starts, py::object ends,
+               const std::string& okey) {
+          const auto d = ints(dims);
+          auto s = ints(starts), e = ints(ends);
+          py::gil_scoped_release release;
+          return self.slice_if(cond, ikey, std::vector<int>(d.begin(), d.end()), std::move(s), std::move(e), okey);
+        },
+        py::arg("cond"), py::arg("ikey"), py::arg("dims"), py::arg("starts"), py::arg("ends"), py::arg(okd) = "");
+  c.def("random_slice_if",
+        [ints](const T& self, bool cond, const std::string& ikey, py::object dims, py::object sizes,
+               const std::string& okey) {
+          const auto d = ints(dims);
+          auto s = ints(sizes);
+          py::gil_scoped_release release;
+          return self.random_slice_if(cond, ikey, std::vector<int>(d.begin(), d.end()), std::move(s), okey);
+        },
+        py::arg("cond"), py::arg("ikey"), py::arg("dims"), py::arg("sizes"), py::arg(okd) = "");
   c.def("pad", &T::pad, nogil(), py::arg("key"), py::arg("dim"), py::arg("lpad"), py::arg("rpad"),
         py::arg("pad_value"), py::arg(okd) = "", "Pad the array at ``key`` along ``dim`` on both sides.");
   c.def("pad_if", &T::pad_if, nogil(), py::arg("cond"), py::arg("key"), py::arg("dim"), py::arg("lpad"),
@@ -366,6 +384,11 @@ void bind_ops(PyClass& c) {
   };
   c.def("sample_transform", sample_transform, py::arg("func"),
         "Apply the python function ``func`` to whole samples (dict in, dict out).");
+  c.def("sample_transform_if",
+        [sample_transform](const T& ds, bool cond, py::function func) {
+          return cond ? sample_transform(ds, std::move(func)) : T(ds.node());
+        },
+        py::arg("cond"), py::arg("func"));
 
   auto key_cast = [](const T& ds, const std::string& key, const std::string& dtype, double scale,
                      std::optional<std::vector<float>> mean, std::optional<std::vector<float>> std_,

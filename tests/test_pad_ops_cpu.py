@@ -101,3 +101,13 @@ def test_slice_ops_match_reference(pkg, case):
         for k in w:
             a, b = np.asarray(g[k]), np.asarray(w[k])
             assert a.shape == b.shape and a.dtype == b.dtype and np.array_equal(a, b), k
+
+
+def test_conditional_twins_of_slice_and_sample_transform(pkg):
+    b = pkg.buffer_from_vector([{"a": np.arange(10, dtype=np.int64)}])
+    assert np.asarray(b.slice_if(True, "a", 0, 2, 5)[0]["a"]).tolist() == [2, 3, 4]
+    assert np.asarray(b.slice_if(False, "a", 0, 2, 5)[0]["a"]).shape == (10,)
+    assert np.asarray(b.random_slice_if(True, "a", 0, 3)[0]["a"]).shape == (3,)
+    assert np.asarray(b.random_slice_if(False, "a", 0, 3)[0]["a"]).shape == (10,)
+    assert np.asarray(b.sample_transform_if(True, lambda s: {"a": s["a"] * 2})[0]["a"])[:3].tolist() == [0, 2, 4]
+    assert np.asarray(b.sample_transform_if(False, lambda s: {})[0]["a"])[:3].tolist() == [0, 1, 2]
