@@ -1,0 +1,96 @@
+"""Seeded random chains through the C ABI against the oracle: random source
+sizes, channel counts, crops and flips on either side of a resize or rotation,
+optional channel reduction, ragged batches, float32 (plain and normalised) and
+uint8 output.  Bit-exact without a resize, within one uint8 step with one."""
+import numpy as np
+import pytest
+
+import chain
+
+pytestmark = pytest.mark.gpu
+
+RESIZE_MISMATCH_MAX = 1e-3
+
+
+def _random_chain(rng, c):
+    ops = []
+    h_lo, w_lo = 24, 24          # every sample is at least 40 x 40, crops stay inside
+
+    def crops_and_flips(hh, ww):
+        out = []
+        k = int(rng.integers(0, 3))
+        for _ in range(k):
+            kind = int(rng.integers(0, 4))
+            if kind < 2 and (hh < 9 or ww < 9):
+                kind = 2          # too small to crop further
+            if kind == 0:
+                hh, ww = int(rng.integers(max(8, hh // 2), hh + 1)), int(rng.integers(max(8, ww // 2), ww + 1))
+                out.append(("image_center_crop", dict(key="image", w=ww, h=hh)))
+            elif kind == 1:
+                hh, ww = int(rng.integers(max(8, hh // 2), hh + 1)), int(rng.integers(max(8, ww // 2), ww + 1))
+                out.append(("image_random_crop", dict(key="image", w=ww, h=hh)))
+            elif kind == 2:
+                out.append(("image_random_h_flip", dict(key="image", prob=0.5)))
+            else:
+                out.append(("image_random_h_flip", dict(key="image", prob=1.0)))
+        return out, hh, ww
+
+    pre, hh, ww = crops_and_flips(h_lo + 16, w_lo + 16)
+    ops += pre
+    geom = int(rng.integers(0, 4))
+    resized = False
+    if geom == 0:
+        tw, th = int(rng.integers(5, 150)), int(rng.integers(5, 150))
+        ops.append(("image_resize", dict(key="image", w=tw, h=th)))
+        hh, ww, resized = th, tw, True
+    elif geom == 1:
+        size = int(rng.integers(12, 120))
+        ops.append(("image_resize_smallest_side", dict(key="image", size=size)))
+        hh = ww = size        # at least `size` on both sides
+        resized = True
+    elif geom == 2:
+        ops.append(("image_rotate", dict(key="image", angle=float(rng.uniform(-60, 60)), crop=bool(rng.integers(0, 2)))))
+        hh, ww = 12, 12       # the rotated, cropped image may be much smaller: keep later crops tiny
+    post, hh, ww = crops_and_flips(hh, ww)
+    ops += post
+    gray = c == 3 and int(rng.integers(0, 4)) == 0
+    if gray:
+        ops.append(("image_channel_reduction", dict(key="image", preset=["default", "rec709", "rec2020", "green"][int(rng.integers(0, 4))])))
+    return ops, resized, gray
+
+
+@pytest.mark.parametrize("seed", range(36))
+def test_random_chain(pkg, ctx, oracle, seed):
+    rng = np.random.default_rng(1000 + seed)
+    c = int(rng.choice([1, 3, 3, 3, 4]))
+    ops, resized, gray = _random_chain(rng, c)
+    n = int(rng.integers(1, 7))
+    samples = [{"image": rng.integers(0, 256, (int(rng.integers(40, 300)), int(rng.integers(40, 300)), c), dtype=np.uint8)}
+               for _ in range(n)]
+    co = 1 if gray else c
+    mode = int(rng.integers(0, 3))
+    if mode == 0:
+        cast = None                                   # uint8 out
+    elif mode == 1:
+        cast = ()
+    else:
+        cast = ([0.485, 0.456, 0.406, 0.5][:co], [0.229, 0.224, 0.225, 0.25][:co])
+    pad = float(rng.integers(0, 256))
+    oracle.set_state(seed)
+    c_arg = None if cast is None else {"image": None if len(cast) == 0 else (np.array(cast[0], np.float32), np.array(cast[1], np.float32))}
+    try:
+        want = [b["image"] for b in oracle.run_chain(samples, ops, n, {"image": pad}, c_arg)]
+    except RuntimeError:
+        pytest.skip("the drawn chain is refused by the reference too (crop larger than the image)")
+    oracle.set_state(seed)
+    got = chain.run_fused(pkg, ctx, samples, "image", ops, n, cast, pad)
+    assert len(got) == len(want) == 1
+    g, w = got[0], want[0]
+    assert g.shape == w.shape and g.dtype == w.dtype, (ops, g.shape, w.shape)
+    if not resized:
+        assert np.array_equal(g, w), ops
+    else:
+        step = 1.0 if cast is None else (1.0 / 255 if len(cast) == 0 else 1.0 / 255 / min(cast[1]))
+        d = np.abs(g.astype(np.float64) - w.astype(np.float64))
+        assert d.max() <= step * 1.0001, ops
+        assert (d > 0).mean() <= RESIZE_MISMATCH_MAX, ops
