@@ -37,6 +37,7 @@ class Buffer : public Dataset<Buffer, buffer::Buffer> {
   Stream ordered_prefetch(int prefetch_size, int num_thread) const;
   Buffer partition(int64_t num_partitions, int64_t partition) const;
   Buffer partition_if(bool cond, int64_t num_partitions, int64_t partition) const;
+  Buffer perm(const std::vector<int64_t>& order) const;
   Buffer shuffle() const;
   Buffer shuffle_if(bool cond) const;
   Stream to_stream();

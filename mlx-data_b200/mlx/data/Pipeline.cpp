@@ -119,6 +119,10 @@ Buffer Buffer::partition_if(bool cond, int64_t num_partitions, int64_t partition
   return cond ? this->partition(num_partitions, partition) : Buffer(self_);
 }
 
+Buffer Buffer::perm(const std::vector<int64_t>& order) const {
+  return Buffer(std::make_shared<buffer::Perm>(self_, order));
+}
+
 Buffer Buffer::shuffle() const {
   return Buffer(buffer::shuffled(self_));
 }

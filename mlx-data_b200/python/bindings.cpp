@@ -568,6 +568,8 @@ PYBIND11_MODULE(_c, m) {
       .def("partition", &Buffer::partition, nogil(), py::arg("num_partitions"), py::arg("partition"))
       .def("partition_if", &Buffer::partition_if, nogil(), py::arg("cond"), py::arg("num_partitions"),
            py::arg("partition"))
+      .def("perm", &Buffer::perm, nogil(), py::arg("perm"),
+           "The samples at the listed indices, in that order (indices may repeat or be left out).")
       .def("shuffle", &Buffer::shuffle, nogil(), "The buffer in a random order (drawn once, here).")
       .def("shuffle_if", &Buffer::shuffle_if, nogil(), py::arg("cond"))
       .def("to_stream", &Buffer::to_stream, nogil());

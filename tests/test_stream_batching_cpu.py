@@ -143,3 +143,15 @@ def test_stream_python_iterable(pkg):
     assert batches[0][0].tolist() == [0, -1, -1, -1]
     with pytest.raises(Exception):
         next(pkg.stream_python_iterable(lambda: iter([3])))
+
+
+def test_buffer_perm(pkg):
+    ref = refpipe.reference_module()
+    samples = [{"x": np.int64(i)} for i in range(6)]
+    order = [5, 0, 0, 3]
+    got = [int(s["x"]) for s in pkg.buffer_from_vector(samples).perm(order)]
+    assert got == order
+    if ref is not None:
+        assert got == [int(s["x"]) for s in ref.buffer_from_vector(samples).perm(order)]
+    with pytest.raises(RuntimeError):
+        pkg.buffer_from_vector(samples).perm([6])
