@@ -68,3 +68,24 @@ def test_dynamic_batch_with_size_buffer(pkg):
     for i in range(len(want)):
         assert np.array_equal(np.asarray(got[i]["id"]), np.asarray(want[i]["id"]))
         assert np.array_equal(np.asarray(got[i]["tokens"]), np.asarray(want[i]["tokens"]))
+
+
+def test_dynamic_batch_sizes_images_without_a_gpu(pkg):
+    """Image ops under a buffer dynamic_batch are sized from their recorded
+    programs: building the batches needs no pixels (and so no GPU); the number
+    of batches equals the reference's, which computes every image to size it."""
+    ref = refpipe.reference_module()
+    if ref is None:
+        pytest.skip("needs the reference compiled under oracle/_ref")
+    rng = np.random.default_rng(12)
+    samples = [{"image": rng.integers(0, 256, (int(rng.integers(20, 140)), int(rng.integers(20, 140)), 3), dtype=np.uint8)}
+               for _ in range(41)]
+
+    def chain(dx):
+        return (dx.buffer_from_vector(samples)
+                .image_resize_smallest_side("image", 32)
+                .slice("image", 1, 0, 50)
+                .pad_to_multiple("image", 0, 8, 0)
+                .dynamic_batch("image", max_data_size=5 * 32 * 64 * 3))
+
+    assert len(chain(pkg)) == len(chain(ref)) > 3
