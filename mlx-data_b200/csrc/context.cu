@@ -277,7 +277,7 @@ int plan_into(const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b, 
       }
     }
     // the float32 kernel needs the largest per-sample sum, the generic one the sum of the largest parts
-    const bool fast = b->out_dtype == MLXD_F32 && b->channels != 2;
+    const bool fast = b->channels != 2;
     if ((fast ? (long long)need.sum_bytes : pass_bytes(need)) <= kPassBudgetBytes) {
       break;
     }

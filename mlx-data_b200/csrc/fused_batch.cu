@@ -453,7 +453,7 @@ cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream) {
 
 void choose_kernel(LaunchParams& p, const PassNeed& need, const DevSample* host_samples, int n) {
   const bool channels_ok = p.c_in == 1 || p.c_in == 3 || p.c_in == 4;
-  p.use_fast = (p.out_f32 && channels_ok && !need.needs_generic) ? 1 : 0;
+  p.use_fast = (channels_ok && !need.needs_generic) ? 1 : 0;
   // The rows below a sample's post window are one contiguous run of its slot;
   // when those runs are at least an eighth of the batch they get a linear fill
   // of their own (pad_fill_kernel), which writes at memory speed.

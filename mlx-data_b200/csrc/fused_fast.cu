@@ -1,13 +1,15 @@
-// The float32-output kernel: one CTA per band of up to eight kTileH x kTileW
-// tiles of one sample's slot, run as a sequence of passes (sub_h x sub_w
-// outputs each).  A resize pass stages its source footprint in shared memory
+// The kernels that run every launch of 1-, 3- and 4-channel images (float32
+// batches, float32 batches after the channel reduction, uint8 batches; 2-channel
+// images stay with the generic kernel in fused_batch.cu): one CTA per band of up
+// to eight kTileH x kTileW tiles of one sample's slot, run as a sequence of
+// passes (sub_h x sub_w outputs each).  A resize pass stages its source footprint in shared memory
 // with bulk asynchronous copies (cp.async.bulk, one per source row, completion
 // on an mbarrier, bounded wait; the next pass's copies are issued as soon as
 // the vertical filter has consumed the buffer), filters vertically - a thread
 // takes eight byte columns into two output rows - into planar float4 columns,
 // filters horizontally - a thread takes one output column of four rows over
-// all channels - quantises, casts through the table and stores straight into
-// the batch tensor.  Copy and nearest-neighbour affine bands read their source
+// all channels - quantises, casts through the table (float32 batches) and
+// stores straight into the batch tensor.  Copy and nearest-neighbour affine bands read their source
 // through the read-only path, four pixels per thread, and store 16 bytes at a
 // time; pad-only bands are plain 16-byte stores.
 //
@@ -473,7 +475,7 @@ __device__ __forceinline__ void start_pass(
 // Geometric-output rows [by, by+nr) (nr <= kTileH) x columns [gx_lo, gx_hi) of
 // a resize sample, sub_w columns per pass, written to the batch tensor.  The
 // copies of pass t+1 are in flight while pass t filters horizontally.
-template <int C, bool GRAY>
+template <int C, bool GRAY, bool U8>
 __device__ void resize_rows(
     const DevSample& s, const LaunchParams& p, const Caps& caps, const Smem& sm, unsigned& parity, bool& first_use,
     int by, int nr, int gx_lo, int gx_hi) {
@@ -741,8 +743,37 @@ __device__ void resize_rows(
           px = s.post_w - 1 - px;
         }
         const int oy = by + rg * 4 - s.post_y;
-        float* dst = base + ((size_t)oy * s.slot_w + px) * CO;
         const int left = nr - rg * 4;
+        if (U8) {
+          // uint8 batch: the quantised pixel (or its channel reduction) as it is
+          unsigned q[4][C];
+#pragma unroll
+          for (int c = 0; c < C; c++) {
+            float a0, a1, a2, a3;
+            unpack2(acc[c][0], a0, a1);
+            unpack2(acc[c][1], a2, a3);
+            q[0][c] = quantise_sat(a0);
+            q[1][c] = quantise_sat(a1);
+            q[2][c] = quantise_sat(a2);
+            q[3][c] = quantise_sat(a3);
+          }
+          uint8_t* dst8 = reinterpret_cast<uint8_t*>(s.dst) + ((size_t)oy * s.slot_w + px) * CO;
+#pragma unroll
+          for (int r = 0; r < 4; r++) {
+            if (r < left) {
+              if (GRAY) {
+                dst8[r * row_stride] = (uint8_t)gray_mix(p, q[r][0], q[r][1 % C], q[r][2 % C]);
+              } else {
+#pragma unroll
+                for (int c = 0; c < C; c++) {
+                  dst8[r * row_stride + c] = (uint8_t)q[r][c];
+                }
+              }
+            }
+          }
+          continue;
+        }
+        float* dst = base + ((size_t)oy * s.slot_w + px) * CO;
         float out[4][CO];
         if (GRAY) {
           // the resized pixel is quantised first, as the image the reference hands
@@ -818,7 +849,7 @@ __device__ __forceinline__ bool affine_source(
 // of a row.  The cast table is read from shared memory (lut_s); the four pixels
 // leave as 16-byte stores when the row segment allows it.  Without a geometric
 // op the four source pixels are adjacent too and come as aligned words.
-template <int C, bool GRAY>
+template <int C, bool GRAY, bool U8>
 __device__ void gather_rows(
     const DevSample& s, const LaunchParams& p, unsigned lut_s, int y0, int vy1, int xa, int xb) {
   constexpr int CO = GRAY ? 1 : C;
@@ -902,6 +933,40 @@ __device__ void gather_rows(
         }
       }
     }
+    if (U8) {
+      // uint8 batch: the 4 * CO bytes as CO aligned words when the row segment allows it
+      unsigned by[4 * CO];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        if (GRAY) {
+          by[j] = gray_mix(p, px[j][0], px[j][1 % C], px[j][2 % C]);
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < C; ch++) {
+            by[(j * CO + ch) % (4 * CO)] = px[j][ch];
+          }
+        }
+      }
+      uint8_t* dst8 = reinterpret_cast<uint8_t*>(s.dst) + ((size_t)(y0 + ry) * s.slot_w + x_first) * CO;
+      if (npx == 4 && (reinterpret_cast<uintptr_t>(dst8) & 3) == 0) {
+#pragma unroll
+        for (int k = 0; k < CO; k++) {
+          reinterpret_cast<uint32_t*>(dst8)[k] =
+              by[4 * k] | (by[4 * k + 1] << 8) | (by[4 * k + 2] << 16) | (by[4 * k + 3] << 24);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          if (j < npx) {
+#pragma unroll
+            for (int ch = 0; ch < CO; ch++) {
+              dst8[j * CO + ch] = (uint8_t)by[j * CO + ch];
+            }
+          }
+        }
+      }
+      continue;
+    }
     float out[4][CO];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
@@ -936,7 +1001,7 @@ __device__ void gather_rows(
 }
 
 // One CTA: rows [y0, y0 + kTileH) of one slot, columns of p.band_tiles tiles.
-template <int C, bool GRAY>
+template <int C, bool GRAY, bool U8>
 __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
   unsigned t = blockIdx.x;
   const int tb = t % p.bands_x;
@@ -961,13 +1026,21 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
   float padf[4];
 #pragma unroll
   for (int c = 0; c < 4; c++) {
-    padf[c] = c < CO ? __ldg(p.lut + c * 256 + p.pad_px) : 0.0f;
+    padf[c] = (!U8 && c < CO) ? __ldg(p.lut + c * 256 + p.pad_px) : 0.0f;
   }
   float* out = reinterpret_cast<float*>(s.dst);
+  // pad value into a rectangle of the slot, float32 or uint8
+  auto pad_rect = [&](int ya, int yb, int xa, int xb) {
+    if (U8) {
+      fill_rect_u8<CO>(reinterpret_cast<uint8_t*>(s.dst), s.slot_w, ya, yb, xa, xb, p.pad_px);
+    } else {
+      fill_rect_f32<CO>(out, s.slot_w, ya, yb, xa, xb, padf);
+    }
+  };
   if (!has_valid) {
     // bands below the post window are pad_fill_kernel's when it runs
     if (!(p.pad_apart && y0 >= s.post_h)) {
-      fill_rect_f32<CO>(out, s.slot_w, y0, y1, x0, x1, padf);
+      pad_rect(y0, y1, x0, x1);
     }
     return;
   }
@@ -979,8 +1052,10 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
   caps.src_tile_bytes = s.need_src;
   Smem sm;
   smem_layout(p.c_out, caps, smem_addr(smem_raw), &sm);
-  for (int i = threadIdx.x; i < CO * 256; i += kThreads) {
-    sp<float>(sm.lut)[i] = __ldg(p.lut + i);
+  if (!U8) {
+    for (int i = threadIdx.x; i < CO * 256; i += kThreads) {
+      sp<float>(sm.lut)[i] = __ldg(p.lut + i);
+    }
   }
   if (s.mode == kModeResize) {
     if (threadIdx.x == 0) {
@@ -999,25 +1074,43 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
     unsigned parity = 0;
     bool first_use = true;
     for (int by = s.post_y + y0; by < s.post_y + vy1; by += s.sub_h) {
-      resize_rows<C, GRAY>(s, p, caps, sm, parity, first_use, by, min(s.sub_h, s.post_y + vy1 - by), gx_lo, gx_hi);
+      resize_rows<C, GRAY, U8>(s, p, caps, sm, parity, first_use, by, min(s.sub_h, s.post_y + vy1 - by), gx_lo, gx_hi);
     }
   } else {
     __syncthreads();
-    gather_rows<C, GRAY>(s, p, sm.lut, y0, vy1, x0, vx1);
+    gather_rows<C, GRAY, U8>(s, p, sm.lut, y0, vy1, x0, vx1);
   }
   // pad the part of the band outside the post window
-  fill_rect_f32<CO>(out, s.slot_w, vy1, y1, x0, x1, padf);
-  fill_rect_f32<CO>(out, s.slot_w, y0, vy1, vx1, x1, padf);
+  pad_rect(vy1, y1, x0, x1);
+  pad_rect(y0, vy1, vx1, x1);
 }
 
 __global__ void __launch_bounds__(kThreads, 3) fused_fast_kernel(const LaunchParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   if (p.c_in == 3) {
-    run_band<3, false>(p, smem_raw);
+    run_band<3, false, false>(p, smem_raw);
   } else if (p.c_in == 1) {
-    run_band<1, false>(p, smem_raw);
+    run_band<1, false, false>(p, smem_raw);
   } else {
-    run_band<4, false>(p, smem_raw);
+    run_band<4, false, false>(p, smem_raw);
+  }
+}
+
+// uint8 batches (no cast): stand-alone ops, images between two geometric ops,
+// pipelines that cast on the host.  Kernels of their own for the same reason
+// as the channel-reduction one.
+__global__ void __launch_bounds__(kThreads, 3) fused_fast_u8_kernel(const LaunchParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  if (p.c_in == 3) {
+    if (p.gray) {
+      run_band<3, true, true>(p, smem_raw);
+    } else {
+      run_band<3, false, true>(p, smem_raw);
+    }
+  } else if (p.c_in == 1) {
+    run_band<1, false, true>(p, smem_raw);
+  } else {
+    run_band<4, false, true>(p, smem_raw);
   }
 }
 
@@ -1076,7 +1169,47 @@ __device__ __forceinline__ void pad_below(const LaunchParams& p) {
   }
 }
 
+// The same for a uint8 batch: a linear fill of bytes.
+__device__ __forceinline__ void pad_below_u8(const LaunchParams& p) {
+  const int n = blockIdx.x / kPadChunks;
+  const int chunk = blockIdx.x - n * kPadChunks;
+  if (n >= p.n) {
+    return;
+  }
+  const DevSample* s = p.samples + n;
+  const int slot_h = s->slot_h, slot_w = s->slot_w;
+  const int post_h = s->post_h < slot_h ? s->post_h : slot_h;
+  const int first_row = ((post_h + kTileH - 1) / kTileH) * kTileH;
+  if (first_row >= slot_h) {
+    return;
+  }
+  const size_t row_bytes = (size_t)slot_w * p.c_out;
+  uint8_t* run = reinterpret_cast<uint8_t*>(s->dst) + (size_t)first_row * row_bytes;
+  const size_t len = (size_t)(slot_h - first_row) * row_bytes;
+  const size_t mis = reinterpret_cast<uintptr_t>(run) & 15;
+  size_t head = (16 - mis) & 15;
+  head = head > len ? len : head;
+  const size_t nvec = (len - head) >> 4;
+  const unsigned w = (unsigned)(p.pad_px & 0xff) * 0x01010101u;
+  const uint4 v = make_uint4(w, w, w, w);
+  const size_t q0 = nvec * (size_t)chunk / kPadChunks;
+  const size_t q1 = nvec * (size_t)(chunk + 1) / kPadChunks;
+  for (size_t q = q0 + threadIdx.x; q < q1; q += kThreads) {
+    *reinterpret_cast<uint4*>(run + head + 16 * q) = v;
+  }
+  if (chunk == 0) {
+    const size_t tail = head + 16 * nvec;
+    for (size_t k = threadIdx.x; k < head + (len - tail); k += kThreads) {
+      run[k < head ? k : tail + (k - head)] = (uint8_t)p.pad_px;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 6) pad_fill_kernel(const LaunchParams p) {
+  if (!p.out_f32) {
+    pad_below_u8(p);
+    return;
+  }
   if (p.c_out == 3) {
     pad_below<3>(p);
   } else if (p.c_out == 1) {
@@ -1090,7 +1223,7 @@ __global__ void __launch_bounds__(kThreads, 6) pad_fill_kernel(const LaunchParam
 // kernel of its own, so that the usual one's register allocation is not touched.
 __global__ void __launch_bounds__(kThreads, 3) fused_fast_gray_kernel(const LaunchParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  run_band<3, true>(p, smem_raw);
+  run_band<3, true, false>(p, smem_raw);
 }
 
 } // namespace
@@ -1115,6 +1248,10 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
       return e;
     }
     e = cudaFuncSetAttribute(fused_fast_gray_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (e != cudaSuccess) {
+      return e;
+    }
+    e = cudaFuncSetAttribute(fused_fast_u8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e != cudaSuccess) {
       return e;
     }
@@ -1150,7 +1287,9 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
       return pe;
     }
   }
-  if (p.gray) {
+  if (!p.out_f32) {
+    fused_fast_u8_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
+  } else if (p.gray) {
     fused_fast_gray_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
   } else {
     fused_fast_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);

@@ -181,4 +181,34 @@ __device__ __forceinline__ void fill_rect_f32(
   }
 }
 
+// The same for a uint8 slot: every byte of the padding is the pad pixel, so the
+// aligned middle of every row goes out as 16-byte stores of one pattern.
+template <int CO>
+__device__ __forceinline__ void fill_rect_u8(
+    uint8_t* base, int slot_w, int ya, int yb, int xa, int xb, int pad_px) {
+  if (ya >= yb || xa >= xb) {
+    return;
+  }
+  const int L = (xb - xa) * CO;
+  const int ny = yb - ya;
+  const size_t row_bytes = (size_t)slot_w * CO;
+  const unsigned w = (unsigned)(pad_px & 0xff) * 0x01010101u;
+  const uint4 v = make_uint4(w, w, w, w);
+  for (int ry = (int)threadIdx.x >> 5; ry < ny; ry += kThreads >> 5) {     // a warp per row
+    uint8_t* rowp = base + (size_t)(ya + ry) * row_bytes + (size_t)xa * CO;
+    const int mis = (int)(reinterpret_cast<uintptr_t>(rowp) & 15);
+    int head = (16 - mis) & 15;
+    head = head > L ? L : head;
+    const int nvec = (L - head) >> 4;
+    const int lane = (int)threadIdx.x & 31;
+    for (int q = lane; q < nvec; q += 32) {
+      *reinterpret_cast<uint4*>(rowp + head + 16 * q) = v;
+    }
+    const int tail = head + 16 * nvec;
+    for (int k = lane; k < head + (L - tail); k += 32) {
+      rowp[k < head ? k : tail + (k - head)] = (uint8_t)pad_px;
+    }
+  }
+}
+
 } // namespace mlxd
