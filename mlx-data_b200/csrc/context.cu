@@ -269,7 +269,7 @@ int plan_into(const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b, 
   // full-size passes at two CTAs per SM are the better deal.
   const long long budgets[3] = {kPassBudgetBytes, kPassBudgetBytes - 8 * 1024, kPassBudgetBytes};
   for (int k = 0; k < 3; k++) {
-    need = PassNeed{0, 0, 0, 0, 0, 0, 0};
+    need = PassNeed{0, 0, 0, 0, 0, 0};
     for (int i = 0; i < n; i++) {
       const int rc = plan_one_sample(samples[i], i, b, out[i], need, budgets[k]);
       if (rc != MLXD_OK) {
@@ -277,7 +277,7 @@ int plan_into(const mlxd_sample_desc* samples, int n, const mlxd_batch_desc* b, 
       }
     }
     // the float32 kernel needs the largest per-sample sum, the generic one the sum of the largest parts
-    const bool fast = b->channels != 2;
+    const bool fast = true;
     if ((fast ? (long long)need.sum_bytes : pass_bytes(need)) <= kPassBudgetBytes) {
       break;
     }

@@ -65,7 +65,6 @@ struct LaunchParams {
   int32_t mid_float4s;
   int32_t weight_floats;
   int32_t u_cap;              // bound on the source rows feeding four adjacent output rows
-  int32_t use_fast;           // 1: the float32 kernel (fused_fast.cu) can run this launch
   int32_t band_tiles;         // float32 kernel: tiles per CTA along a row band (set at launch)
   int32_t bands_x;            // float32 kernel: CTAs per row band
   int32_t fast_smem_bytes;    // float32 kernel: dynamic shared memory of the launch
@@ -79,25 +78,22 @@ struct PassNeed {
   int32_t mid_float4s;
   int32_t weight_floats;
   int32_t u_cap;
-  int32_t needs_generic;      // a sample only the generic kernel handles (none at present)
   int64_t sum_bytes;          // largest per-sample sum of the parts that grow with the pass (pass_bytes)
   int64_t fast_smem_bytes;    // float32 kernel: largest per-sample shared-memory layout
 };
-
-// Bytes of dynamic shared memory the kernel needs for these parameters.
-size_t fused_batch_smem_bytes(const LaunchParams& p);
 
 // Dynamic shared memory of the float32 kernel for a sample with these needs
 // (c_out channels in the cast table).
 size_t fused_fast_layout_bytes(int c_out, int u_cap, int weight_floats, int mid_float4s, int src_tile_bytes);
 
-// Launch the float32 kernel when p.use_fast is set, else the generic one.
+// Launch the band kernel that fits the parameters (float32, float32 after the
+// channel reduction, uint8, two channels), preceded by pad_fill_kernel when
+// p.pad_apart is set.
 cudaError_t launch_fused_batch(const LaunchParams& p, cudaStream_t stream);
 cudaError_t launch_fused_fast(const LaunchParams& p, cudaStream_t stream);
 
-// Decide which kernel runs a launch, and whether a ragged batch's padding gets
-// a launch of its own; call after the planner filled `need` and the host copy
-// of the sample table.
+// Decide whether a ragged batch's padding gets a launch of its own; call after
+// the planner filled `need` and the host copy of the sample table.
 void choose_kernel(LaunchParams& p, const PassNeed& need, const DevSample* host_samples, int n);
 
 // Conservative per-axis bounds used by the host planner.

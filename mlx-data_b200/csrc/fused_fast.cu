@@ -771,8 +771,7 @@ __device__ void resize_rows(
               }
             }
           }
-          continue;
-        }
+        } else {
         float* dst = base + ((size_t)oy * s.slot_w + px) * CO;
         float out[4][CO];
         if (GRAY) {
@@ -811,6 +810,7 @@ __device__ void resize_rows(
           if (r < left) {
             store_pixel<CO>(dst + r * row_stride, out[r], vec_ok);
           }
+        }
         }
       }
     }
@@ -965,8 +965,7 @@ __device__ void gather_rows(
           }
         }
       }
-      continue;
-    }
+    } else {
     float out[4][CO];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
@@ -996,6 +995,7 @@ __device__ void gather_rows(
           }
         }
       }
+    }
     }
   }
 }
@@ -1096,6 +1096,13 @@ __global__ void __launch_bounds__(kThreads, 3) fused_fast_kernel(const LaunchPar
   }
 }
 
+// Two-channel images, float32 batches.  Rare; kept out of the kernel above so
+// that its register allocation is decided by the common cases alone.
+__global__ void __launch_bounds__(kThreads, 3) fused_fast_c2_kernel(const LaunchParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  run_band<2, false, false>(p, smem_raw);
+}
+
 // uint8 batches (no cast): stand-alone ops, images between two geometric ops,
 // pipelines that cast on the host.  Kernels of their own for the same reason
 // as the channel-reduction one.
@@ -1109,6 +1116,8 @@ __global__ void __launch_bounds__(kThreads, 3) fused_fast_u8_kernel(const Launch
     }
   } else if (p.c_in == 1) {
     run_band<1, false, true>(p, smem_raw);
+  } else if (p.c_in == 2) {
+    run_band<2, false, true>(p, smem_raw);
   } else {
     run_band<4, false, true>(p, smem_raw);
   }
@@ -1214,6 +1223,8 @@ __global__ void __launch_bounds__(kThreads, 6) pad_fill_kernel(const LaunchParam
     pad_below<3>(p);
   } else if (p.c_out == 1) {
     pad_below<1>(p);
+  } else if (p.c_out == 2) {
+    pad_below<2>(p);
   } else {
     pad_below<4>(p);
   }
@@ -1255,6 +1266,10 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
     if (e != cudaSuccess) {
       return e;
     }
+    e = cudaFuncSetAttribute(fused_fast_c2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (e != cudaSuccess) {
+      return e;
+    }
     e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) {
       return e;
@@ -1289,6 +1304,8 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
   }
   if (!p.out_f32) {
     fused_fast_u8_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
+  } else if (p.c_in == 2) {
+    fused_fast_c2_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
   } else if (p.gray) {
     fused_fast_gray_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
   } else {

@@ -122,7 +122,7 @@ extern "C" int mlxd_fused_batch_noalloc(
   p.lut = reinterpret_cast<const float*>(scratch + kTableBytes);
   p.status = reinterpret_cast<int32_t*>(scratch + kStatusOffset);
 
-  PassNeed need = PassNeed{0, 0, 0, 0, 0, 0, 0};
+  PassNeed need = PassNeed{0, 0, 0, 0, 0, 0};
   const size_t esize = p.out_f32 ? 4 : 1;
   const size_t slot_bytes = (size_t)batch->slot_h * batch->slot_w * p.c_out * esize;
   rc = plan_into(samples, n, batch, table, need);
