@@ -10,6 +10,8 @@
 //   channel_reduction  mlx/data/core/image/ImageTransform.cpp:142-182
 //   batch + pad        mlx/data/Array.cpp:465-498, mlx/data/core/BatchShape.cpp:26-45
 //   cast               README.md:55-57 (x.astype(float32) / 255 and its normalised form)
+#include <cmath>
+
 #include "fused_batch.h"
 
 namespace mlxd {
@@ -44,10 +46,13 @@ AxisPlan plan_axis(int32_t n_src, int32_t n_dst, int32_t sub) {
     a.extent = sub + 4;
     return a;
   }
-  const int r = (n_src + n_dst - 1) / n_dst;  // ceil of the shrink ratio
-  a.cap = 2 * r + 3;
-  const long long span = ((long long)sub * n_src + n_dst - 1) / n_dst;
-  a.extent = (int32_t)(span + 2 * r + 3);
+  // Output o reads taps ceil(u - R) .. floor(u + R) with u = (o + 0.5) * ratio - 0.5
+  // and R = ratio: at most floor(2R) + 1 of them, and `sub` consecutive
+  // outputs span at most (sub - 1) * ratio + 2R + 1 source samples.  One more
+  // of each covers the float32 rounding of u and R in the kernel.
+  const double ratio = (double)n_src / (double)n_dst;
+  a.cap = (int32_t)std::floor(2.0 * ratio) + 2;
+  a.extent = (int32_t)std::ceil((double)(sub - 1) * ratio + 2.0 * ratio) + 2;
   return a;
 }
 
