@@ -1,22 +1,25 @@
 // The kernels that run every launch (float32 batches, float32 batches after the
 // channel reduction, two-channel float32 batches, uint8 batches; one entry point
 // each, the same code): one CTA per band of up to eight kTileH x kTileW tiles of
-// one sample's slot, run as a sequence of passes (sub_h x sub_w outputs each).  A resize pass stages its source footprint in shared memory
-// with bulk asynchronous copies (cp.async.bulk, one per source row, completion
-// on an mbarrier, bounded wait; the next pass's copies are issued as soon as
-// the vertical filter has consumed the buffer), filters vertically - a thread
-// takes eight byte columns into two output rows - into planar float4 columns,
-// filters horizontally - a thread takes one output column of four rows over
-// all channels - quantises, casts through the table (float32 batches) and
-// stores straight into the batch tensor.  Copy and nearest-neighbour affine bands read their source
-// through the read-only path, four pixels per thread, and store 16 bytes at a
-// time; pad-only bands are plain 16-byte stores.
+// one sample's slot, run as a sequence of passes (sub_h x sub_w outputs each).
+// A resize pass stages its source footprint in shared memory with bulk
+// asynchronous copies (cp.async.bulk, one per source row, completion on an
+// mbarrier, bounded wait; the next pass's copies are issued as soon as the
+// vertical filter has consumed the buffer), filters vertically - a thread takes
+// eight byte columns into two output rows - into planar float4 columns, filters
+// horizontally - a thread takes one output column of four rows over all
+// channels - quantises, casts through the table (float32 batches) and stores
+// straight into the batch tensor.  Copy and nearest-neighbour affine bands read
+// their source through the read-only path, four pixels per thread, and store
+// 16 bytes at a time; pad-only bands are plain 16-byte stores, and the rows
+// below a sample in a ragged batch go out through a linear fill kernel.
 //
-// The arithmetic: every resize output is a chain acc = fma(w_k, v_k, acc) from 0 in increasing tap order,
-// vertical axis first, quantised as (int)(acc + 0.5) clamped to [0, 255].  The
-// vertical pass walks the union of the source rows of its two output rows; a
-// row that is not a tap of one of them enters that output with weight 0, which
-// leaves its accumulator unchanged, so every chain is the same.
+// The arithmetic: every resize output is a chain acc = fma(w_k, v_k, acc) from
+// 0 in increasing tap order, vertical axis first, quantised as (int)(acc + 0.5)
+// clamped to [0, 255].  The vertical pass walks the union of the source rows of
+// its two output rows; a row that is not a tap of one of them enters that
+// output with weight 0, which leaves its accumulator unchanged, so every chain
+// is the same.
 #include "fused_batch.h"
 #include "kernel_common.cuh"
 
