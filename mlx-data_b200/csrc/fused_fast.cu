@@ -93,6 +93,12 @@ __device__ __forceinline__ void ffma2(f32x2& d, f32x2 a, f32x2 b) {
   asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
 }
 
+__device__ __forceinline__ f32x2 fmul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 __device__ __forceinline__ f32x2 pack2(float lo, float hi) {
   f32x2 r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
@@ -234,6 +240,49 @@ __device__ __forceinline__ void octet_offsets(int j0, int pslots, unsigned (&b)[
   }
 }
 
+// One union row of vertical_taps into the eight accumulators: the two words at
+// shared address ra (funnel-shifted by sh when SHIFT), the row's weights at wp.
+// FIRST: products instead of multiply-adds onto zero.  Pixels and weights are
+// never negative, so the product is the same float, +0 included.
+template <bool SHIFT, bool FIRST>
+__device__ __forceinline__ void vertical_row(unsigned ra, unsigned sh, unsigned wp, f32x2 minus_two23, f32x2 (&acc)[8]) {
+  f32x2 w0, w1;
+  lds_v2u64<0>(wp, w0, w1);
+  uint32_t wa, wb;
+  if (SHIFT) {
+    const uint32_t x0 = lds_u32<0>(ra);
+    const uint32_t x1 = lds_u32<4>(ra);
+    const uint32_t x2 = lds_u32<8>(ra);
+    wa = __funnelshift_r(x0, x1, sh);
+    wb = __funnelshift_r(x1, x2, sh);
+  } else {
+    lds_v2u32<0>(ra, wa, wb);
+  }
+  const f32x2 v0 = bytes_to_f32x2<0, 1>(wa, minus_two23);
+  const f32x2 v1 = bytes_to_f32x2<2, 3>(wa, minus_two23);
+  const f32x2 v2 = bytes_to_f32x2<0, 1>(wb, minus_two23);
+  const f32x2 v3 = bytes_to_f32x2<2, 3>(wb, minus_two23);
+  if (FIRST) {
+    acc[0] = fmul2(v0, w0);
+    acc[1] = fmul2(v1, w0);
+    acc[2] = fmul2(v0, w1);
+    acc[3] = fmul2(v1, w1);
+    acc[4] = fmul2(v2, w0);
+    acc[5] = fmul2(v3, w0);
+    acc[6] = fmul2(v2, w1);
+    acc[7] = fmul2(v3, w1);
+  } else {
+    ffma2(acc[0], v0, w0);
+    ffma2(acc[1], v1, w0);
+    ffma2(acc[2], v0, w1);
+    ffma2(acc[3], v1, w1);
+    ffma2(acc[4], v2, w0);
+    ffma2(acc[5], v3, w0);
+    ffma2(acc[6], v2, w1);
+    ffma2(acc[7], v3, w1);
+  }
+}
+
 // Vertical taps of eight adjacent byte columns (two source words) into a pair
 // of output rows.  acc[4 * h + 2 * r + k] holds, for word h and row r of the
 // pair, the byte pair (2k, 2k+1).  up walks the {row address, funnel shift}
@@ -244,38 +293,26 @@ template <bool SHIFT>
 __device__ __forceinline__ void vertical_taps(unsigned up, unsigned wp, unsigned g8, int cnt, f32x2 (&acc)[8]) {
   const f32x2 minus_two23 = pack2(-8388608.0f, -8388608.0f);
   const unsigned up_end = up + 8u * (unsigned)cnt;
+  // The table entry of the next row is fetched while this row is filtered, so
+  // a row's loads do not wait for one another.  The entry after the last row
+  // is read and dropped: it lies inside the table set whatever cnt is.
+  uint32_t ra, sh;
+  lds_v2u32<0>(up, ra, sh);
+  {
+    uint32_t ra_n, sh_n;
+    lds_v2u32<8>(up, ra_n, sh_n);
+    vertical_row<SHIFT, true>(ra + g8, sh, wp, minus_two23, acc);
+    ra = ra_n;
+    sh = sh_n;
+    up += 8;
+    wp += 16;
+  }
   while (up != up_end) {
-    uint32_t ra, sh;
-    lds_v2u32<0>(up, ra, sh);
-    f32x2 w0, w1;
-    lds_v2u64<0>(wp, w0, w1);
-    ra += g8;
-    uint32_t wa, wb;
-    if (SHIFT) {
-      const uint32_t x0 = lds_u32<0>(ra);
-      const uint32_t x1 = lds_u32<4>(ra);
-      const uint32_t x2 = lds_u32<8>(ra);
-      wa = __funnelshift_r(x0, x1, sh);
-      wb = __funnelshift_r(x1, x2, sh);
-    } else {
-      lds_v2u32<0>(ra, wa, wb);
-    }
-    {
-      const f32x2 va = bytes_to_f32x2<0, 1>(wa, minus_two23);
-      const f32x2 vb = bytes_to_f32x2<2, 3>(wa, minus_two23);
-      ffma2(acc[0], va, w0);
-      ffma2(acc[1], vb, w0);
-      ffma2(acc[2], va, w1);
-      ffma2(acc[3], vb, w1);
-    }
-    {
-      const f32x2 va = bytes_to_f32x2<0, 1>(wb, minus_two23);
-      const f32x2 vb = bytes_to_f32x2<2, 3>(wb, minus_two23);
-      ffma2(acc[4], va, w0);
-      ffma2(acc[5], vb, w0);
-      ffma2(acc[6], va, w1);
-      ffma2(acc[7], vb, w1);
-    }
+    uint32_t ra_n, sh_n;
+    lds_v2u32<8>(up, ra_n, sh_n);
+    vertical_row<SHIFT, false>(ra + g8, sh, wp, minus_two23, acc);
+    ra = ra_n;
+    sh = sh_n;
     up += 8;
     wp += 16;
   }
@@ -601,7 +638,7 @@ __device__ void resize_rows(
           octet_offsets<C>(j0, pslots, b0, low);
           for (int rp = tid >> 6; rp < nrp; rp += kThreads >> 6) {
             const int cnt = sp<int>(sm.ucount)[rp];
-            f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            f32x2 acc[8];
             if (cur.shifted) {
               vertical_taps<true>(urow_base + rp * caps.u_cap * 8, uw_base + rp * caps.u_cap * 16, 8u * g, cnt, acc);
             } else {
@@ -625,7 +662,7 @@ __device__ void resize_rows(
           rp += ((rp + 1) * np <= i) ? 1 : 0;
           const int g = i - rp * np;
           const int cnt = sp<int>(sm.ucount)[rp];
-          f32x2 acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          f32x2 acc[8];
           if (cur.shifted) {
             vertical_taps<true>(urow_base + rp * caps.u_cap * 8, uw_base + rp * caps.u_cap * 16, 8u * g, cnt, acc);
           } else {
