@@ -197,13 +197,17 @@ static int plan_resize(DevSample& s, int C, int i, PassNeed& need, long long pas
       } else if (sub_w > 1) {
         sub_w /= 2;
       } else {
-        return fail(
-            MLXD_ERR_UNSUPPORTED,
-            "sample " + std::to_string(i) + ": shrink ratio too large for the on-chip filter footprint");
+        break;
       }
     }
   }
-  return fail(MLXD_ERR_UNSUPPORTED, "sample " + std::to_string(i) + ": no pass size fits");
+  // No pass size holds the taps of even one output: the sample is filtered
+  // pixel by pixel from global memory instead.
+  (void)i;
+  s.mode = kModeResizeDirect;
+  s.cap_y = plan_axis(s.pre_h, s.geom_h, 1).cap;
+  s.cap_x = plan_axis(s.pre_w, s.geom_w, 1).cap;
+  return MLXD_OK;
 }
 
 int plan_one_sample(
@@ -315,7 +319,7 @@ void needed_region(const DevSample& s, int margin, int32_t& r0, int32_t& r1, int
     rhi = (int64_t)s.post_y + s.post_h;
     clo = s.post_x;
     chi = (int64_t)s.post_x + s.post_w;
-  } else if (s.mode == kModeResize) {
+  } else if (s.mode == kModeResize || s.mode == kModeResizeDirect) {
     axis_span(s.pre_h, s.geom_h, s.post_y, (int64_t)s.post_y + s.post_h, margin, rlo, rhi);
     axis_span(s.pre_w, s.geom_w, s.post_x, (int64_t)s.post_x + s.post_w, margin, clo, chi);
     if (s.pre_flip) {

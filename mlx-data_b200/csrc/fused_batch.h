@@ -20,7 +20,10 @@ constexpr int kMidFloats = 12 * 1024;      // vertically filtered values, float3
 constexpr int kWeightFloats = 2 * 1024;    // tap weights of both axes
 constexpr int kMaxStagedRows = 192;        // source rows per pass
 
-enum Mode : int32_t { kModeCopy = 0, kModeResize = 1, kModeAffine = 2 };
+// kModeResizeDirect: a resize whose tap footprint does not fit the on-chip
+// passes at any pass size (shrink ratios of about 60 and more); every output
+// pixel is then filtered straight from global memory by resize_direct_kernel.
+enum Mode : int32_t { kModeCopy = 0, kModeResize = 1, kModeAffine = 2, kModeResizeDirect = 3 };
 
 // One sample's program.  Coordinates name four nested images:
 //   source [src_h, src_w] -> pre window [pre_h, pre_w] (+mirror)
@@ -69,6 +72,7 @@ struct LaunchParams {
   int32_t bands_x;            // float32 kernel: CTAs per row band
   int32_t fast_smem_bytes;    // float32 kernel: dynamic shared memory of the launch
   int32_t pad_apart;          // float32 kernel: the rows below each post window are written by pad_fill_kernel
+  int32_t direct;             // some sample is kModeResizeDirect: resize_direct_kernel runs after the band kernel
   int32_t starve_wait;        // test hook: the first pass of every band expects 16 bytes that no copy delivers
 };
 

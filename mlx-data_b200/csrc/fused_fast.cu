@@ -12,7 +12,9 @@
 // straight into the batch tensor.  Copy and nearest-neighbour affine bands read
 // their source through the read-only path, four pixels per thread, and store
 // 16 bytes at a time; pad-only bands are plain 16-byte stores, and the rows
-// below a sample in a ragged batch go out through a linear fill kernel.
+// below a sample in a ragged batch go out through a linear fill kernel.  A
+// resize whose taps fit no pass size (shrink ratios of about 60 and more) is
+// filtered pixel by pixel from global memory by a kernel of its own.
 //
 // The arithmetic: every resize output is a chain acc = fma(w_k, v_k, acc) from
 // 0 in increasing tap order, vertical axis first, quantised as (int)(acc + 0.5)
@@ -1114,10 +1116,11 @@ __device__ void run_band(const LaunchParams& p, unsigned char* smem_raw) {
     for (int by = s.post_y + y0; by < s.post_y + vy1; by += s.sub_h) {
       resize_rows<C, GRAY, U8>(s, p, caps, sm, parity, first_use, by, min(s.sub_h, s.post_y + vy1 - by), gx_lo, gx_hi);
     }
-  } else {
+  } else if (s.mode != kModeResizeDirect) {
     __syncthreads();
     gather_rows<C, GRAY, U8>(s, p, sm.lut, y0, vy1, x0, vx1);
   }
+  // (the post window of a kModeResizeDirect sample is resize_direct_kernel's)
   // pad the part of the band outside the post window
   pad_rect(vy1, y1, x0, x1);
   pad_rect(y0, vy1, vx1, x1);
@@ -1277,6 +1280,119 @@ __global__ void __launch_bounds__(kThreads, 3) fused_fast_gray_kernel(const Laun
 
 } // namespace
 
+// ---- resizes whose taps do not fit the on-chip passes ---------------------------------
+//
+// One thread per pixel of the post window, every tap read from global memory.
+// The arithmetic is that of the band kernel, value by value: per source column
+// the vertical sum (first tap a product, then multiply-adds in tap order, taps
+// outside the window reading the clamped row), then the horizontal
+// multiply-adds over those sums in tap order onto zero, weights tent / sum
+// with the sum taken in tap order.  Such samples are rare and small on the
+// output side (a shrink ratio of 60 or more), so nothing is staged or shared.
+template <int C>
+__device__ void direct_pixel(const DevSample& s, const LaunchParams& p, int ox, int oy) {
+  const Axis ay = make_axis(s.pre_h, s.geom_h);
+  const Axis ax = make_axis(s.pre_w, s.geom_w);
+  const int gy = s.post_y + oy;
+  const int gx = s.post_x + (s.post_flip ? s.post_w - 1 - ox : ox);
+  int ylo, yhi, xlo, xhi;
+  axis_range(ay, gy, ylo, yhi);
+  axis_range(ax, gx, xlo, xhi);
+  const int cy = yhi - ylo + 1;
+  int cx = xhi - xlo + 1;
+  cx = cx > s.cap_x ? s.cap_x : cx;
+  const float uy = axis_center(ay, gy);
+  const float ux = axis_center(ax, gx);
+  float sum_y = 0.0f, sum_x = 0.0f;
+  if (!ay.identity) {
+    for (int k = 0; k < cy; k++) {
+      sum_y = __fadd_rn(sum_y, axis_tent(ay, uy, ylo + k));
+    }
+  }
+  if (!ax.identity) {
+    for (int j = 0; j < cx; j++) {
+      sum_x = __fadd_rn(sum_x, axis_tent(ax, ux, xlo + j));
+    }
+  }
+  float acc_h[C];
+#pragma unroll
+  for (int c = 0; c < C; c++) {
+    acc_h[c] = 0.0f;
+  }
+  for (int j = 0; j < cx; j++) {
+    const float wx = ax.identity ? 1.0f : __fdiv_rn(axis_tent(ax, ux, xlo + j), sum_x);
+    const int seen = clampi(xlo + j, 0, s.pre_w - 1);
+    const int col = s.pre_x + (s.pre_flip ? s.pre_w - 1 - seen : seen);
+    float acc_v[C];
+#pragma unroll
+    for (int c = 0; c < C; c++) {
+      acc_v[c] = 0.0f;
+    }
+    for (int k = 0; k < cy; k++) {
+      const float wy = ay.identity ? 1.0f : __fdiv_rn(axis_tent(ay, uy, ylo + k), sum_y);
+      const int row = s.pre_y + clampi(ylo + k, 0, s.pre_h - 1);
+      const uint8_t* px = s.src + ((size_t)row * s.src_w + col) * C;
+#pragma unroll
+      for (int c = 0; c < C; c++) {
+        const float v = (float)__ldg(px + c);
+        acc_v[c] = k == 0 ? __fmul_rn(v, wy) : __fmaf_rn(v, wy, acc_v[c]);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < C; c++) {
+      acc_h[c] = __fmaf_rn(acc_v[c], wx, acc_h[c]);
+    }
+  }
+  unsigned q[C];
+#pragma unroll
+  for (int c = 0; c < C; c++) {
+    q[c] = quantise_sat(acc_h[c]);
+  }
+  const size_t at = (size_t)oy * s.slot_w + ox;
+  if (p.gray) {
+    const unsigned g = gray_mix(p, q[0], q[1 % C], q[2 % C]);
+    if (p.out_f32) {
+      reinterpret_cast<float*>(s.dst)[at] = __ldg(p.lut + g);
+    } else {
+      reinterpret_cast<uint8_t*>(s.dst)[at] = (uint8_t)g;
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < C; c++) {
+      if (p.out_f32) {
+        reinterpret_cast<float*>(s.dst)[at * C + c] = __ldg(p.lut + c * 256 + q[c]);
+      } else {
+        reinterpret_cast<uint8_t*>(s.dst)[at * C + c] = (uint8_t)q[c];
+      }
+    }
+  }
+}
+
+constexpr int kDirectChunks = 64;   // CTAs per sample
+
+__global__ void __launch_bounds__(kThreads) resize_direct_kernel(const LaunchParams p) {
+  const DevSample& s = p.samples[blockIdx.y];
+  if (s.mode != kModeResizeDirect) {
+    return;
+  }
+  const int vh = s.post_h < s.slot_h ? s.post_h : s.slot_h;
+  const int vw = s.post_w < s.slot_w ? s.post_w : s.slot_w;
+  const long long count = (long long)vh * vw;
+  for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < count; i += (long long)kDirectChunks * kThreads) {
+    const int oy = (int)(i / vw);
+    const int ox = (int)(i - (long long)oy * vw);
+    if (p.c_in == 3) {
+      direct_pixel<3>(s, p, ox, oy);
+    } else if (p.c_in == 1) {
+      direct_pixel<1>(s, p, ox, oy);
+    } else if (p.c_in == 2) {
+      direct_pixel<2>(s, p, ox, oy);
+    } else {
+      direct_pixel<4>(s, p, ox, oy);
+    }
+  }
+}
+
 size_t fused_fast_layout_bytes(int c_out, int u_cap, int weight_floats, int mid_float4s, int src_tile_bytes) {
   const Caps caps{u_cap, weight_floats, mid_float4s, src_tile_bytes};
   return smem_layout(c_out, caps, 0u, nullptr);   // without a resize only the cast table
@@ -1348,6 +1464,13 @@ cudaError_t launch_fused_fast(const LaunchParams& p_in, cudaStream_t stream) {
     fused_fast_gray_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
   } else {
     fused_fast_kernel<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
+  }
+  if (p.direct) {
+    const cudaError_t be = cudaGetLastError();
+    if (be != cudaSuccess) {
+      return be;
+    }
+    resize_direct_kernel<<<dim3(kDirectChunks, (unsigned)p.n), kThreads, 0, stream>>>(p);
   }
   return cudaGetLastError();
 }

@@ -26,6 +26,12 @@ void choose_kernel(LaunchParams& p, const PassNeed& need, const DevSample* host_
   // when those runs are at least an eighth of the batch they get a linear fill
   // of their own (pad_fill_kernel), which writes at memory speed.
   p.pad_apart = 0;
+  p.direct = 0;
+  for (int i = 0; i < n; i++) {
+    if (host_samples[i].mode == kModeResizeDirect) {
+      p.direct = 1;
+    }
+  }
   if (n > 0) {
     unsigned long long rows = 0, below = 0;
     for (int i = 0; i < n; i++) {

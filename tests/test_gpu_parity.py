@@ -311,6 +311,49 @@ def test_float32_resize_cases(pkg, ctx, oracle, case, cast):
     _compare(got, want, True, cast)
 
 
+# ---------------------------------------------------------------- shrink ratios beyond the on-chip passes
+DIRECT_RESIZE_CASES = [
+    # one output row of these takes more source rows (2 * ratio + 1) than a pass can stage (192): every
+    # pixel is filtered from global memory by the kernel for such samples
+    ((1500, 1500), 3, [("image_resize", dict(key="image", w=12, h=12))]),
+    ((2100, 64), 1, [("image_resize", dict(key="image", w=32, h=10))]),
+    ((1300, 900), 4, [("image_random_h_flip", dict(key="image", prob=1.0)),
+                      ("image_resize", dict(key="image", w=9, h=7)),
+                      ("image_center_crop", dict(key="image", w=5, h=5))]),
+    ((1200, 301), 3, [("image_resize", dict(key="image", w=11, h=4)),
+                      ("image_random_h_flip", dict(key="image", prob=1.0))]),
+    ((1000, 40), 2, [("image_resize", dict(key="image", w=40, h=5))]),
+]
+
+
+@pytest.mark.parametrize("case", range(len(DIRECT_RESIZE_CASES)))
+@pytest.mark.parametrize("cast", [None, (), "norm"])
+def test_resize_beyond_the_on_chip_footprint(pkg, ctx, oracle, case, cast):
+    """A batch of two such samples and one small image that takes the staged
+    passes, same chain: uint8, float32 and normalised float32 out."""
+    (h, w), c, ops = DIRECT_RESIZE_CASES[case]
+    rng = np.random.default_rng(500 + case)
+    shapes = [(h, w), (h - 7, w - 3), (57, 64)]
+    samples = [{"image": rng.integers(0, 256, (a, b, c), dtype=np.uint8)} for a, b in shapes]
+    if cast == "norm":
+        cast = ([0.485, 0.456, 0.406, 0.5][:c], [0.229, 0.224, 0.225, 0.25][:c])
+    want = _oracle_batches(oracle, samples, ops, 3, cast, 3.0)
+    got = _fused_batches(pkg, ctx, oracle, samples, ops, 3, cast, 3.0)
+    _compare(got, want, True, cast)
+
+
+def test_resize_beyond_the_on_chip_footprint_gray(pkg, ctx, oracle):
+    ops = [("image_resize", dict(key="image", w=14, h=9)),
+           ("image_channel_reduction", dict(key="image", preset="default"))]
+    rng = np.random.default_rng(77)
+    samples = [{"image": rng.integers(0, 256, s, dtype=np.uint8)} for s in [(1100, 1400, 3), (90, 70, 3)]]
+    for cast in (None, ()):
+        want = _oracle_batches(oracle, samples, ops, 2, cast, 0.0)
+        got = _fused_batches(pkg, ctx, oracle, samples, ops, 2, cast, 0.0)
+        assert got[0].shape[-1] == 1
+        _compare(got, want, True, cast)
+
+
 # ---------------------------------------------------------------- float32 kernel, channel reduction
 GRAY_CASES = [
     [("image_resize", dict(key="image", w=61, h=47)),

@@ -96,6 +96,21 @@ def test_prefetch_threads_deterministic_chain(pkg):
         _check([b], [by_first[int(b["label"][0])]], True, 1.0 / 255)
 
 
+def test_thumbnails_of_large_images(pkg):
+    """Shrink ratios of 100 and more, beyond what the staged resize passes hold:
+    the chain still runs as one fused batch and equals the reference pipeline."""
+    rng = np.random.default_rng(21)
+    shapes = [(1400, 1900, 3), (1300, 1700, 3), (120, 90, 3), (1999, 1203, 3)]
+    samples = [{"image": rng.integers(0, 256, s, dtype=np.uint8)} for s in shapes]
+    ops = [("image_resize_smallest_side", dict(key="image", size=10)),
+           ("image_center_crop", dict(key="image", w=10, h=10)),
+           ("image_random_h_flip", dict(key="image", prob=0.5))]
+    want = refpipe.run_reference(samples, ops, 4, {"image": 0.0}, {"image": ()}, seed=2)
+    pkg.core.set_state(2)
+    got = [dict(b) for b in refpipe.build(pkg, samples, ops, 4, {"image": 0.0}, {"image": ()}, native_cast=True)]
+    _check(got, want, True, 1.0 / 255)
+
+
 def test_unfused_ops_one_by_one(pkg):
     """Ops applied without a batch node run as single launches and still match."""
     rng = np.random.default_rng(8)
