@@ -31,7 +31,7 @@ enum mlxd_status {
   MLXD_ERR_CUDA = 2,        /* a CUDA call failed; message carries its text */
   MLXD_ERR_NOMEM = 3,       /* host or device allocation failed */
   MLXD_ERR_TIMEOUT = 4,     /* mlxd_batch_wait ran out of time; work still queued */
-  MLXD_ERR_UNSUPPORTED = 5, /* a shape this build cannot run on the device */
+  MLXD_ERR_UNSUPPORTED = 5, /* a shape the device code cannot run (kept for callers; nothing returns it now) */
   MLXD_ERR_DEVICE = 6       /* the kernel recorded a failed self-check */
 };
 
