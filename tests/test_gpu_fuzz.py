@@ -94,3 +94,47 @@ def test_random_chain(pkg, ctx, oracle, seed):
         d = np.abs(g.astype(np.float64) - w.astype(np.float64))
         assert d.max() <= step * 1.0001, ops
         assert (d > 0).mean() <= RESIZE_MISMATCH_MAX, ops
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_thumbnail_chain(pkg, ctx, oracle, seed):
+    """Large sources down to a few pixels: shrink ratios far beyond what a
+    resize pass can stage (mixed with moderate ones in the same batch)."""
+    rng = np.random.default_rng(9000 + seed)
+    c = int(rng.choice([1, 2, 3, 3, 4]))
+    n = int(rng.integers(1, 4))
+    samples = []
+    for _ in range(n):
+        big, other = int(rng.integers(700, 2600)), int(rng.integers(30, 2600))
+        h, w = (big, other) if rng.integers(0, 2) else (other, big)
+        samples.append({"image": rng.integers(0, 256, (h, w, c), dtype=np.uint8)})
+    ops = []
+    if rng.integers(0, 2):
+        ops.append(("image_random_h_flip", dict(key="image", prob=float(rng.choice([0.5, 1.0])))))
+    tw, th = int(rng.integers(2, 24)), int(rng.integers(2, 24))
+    if rng.integers(0, 3) == 0:
+        ops.append(("image_resize_smallest_side", dict(key="image", size=int(rng.integers(2, 16)))))
+    else:
+        ops.append(("image_resize", dict(key="image", w=tw, h=th)))
+        if rng.integers(0, 2):
+            ops.append(("image_center_crop", dict(key="image", w=max(1, tw - 1), h=max(1, th - 1))))
+    if rng.integers(0, 2):
+        ops.append(("image_random_h_flip", dict(key="image", prob=float(rng.choice([0.5, 1.0])))))
+    gray = c == 3 and int(rng.integers(0, 3)) == 0
+    if gray:
+        ops.append(("image_channel_reduction", dict(key="image", preset="default")))
+    co = 1 if gray else c
+    mode = int(rng.integers(0, 3))
+    cast = None if mode == 0 else (() if mode == 1 else ([0.485, 0.456, 0.406, 0.5][:co], [0.229, 0.224, 0.225, 0.25][:co]))
+    pad = float(rng.integers(0, 256))
+    c_arg = None if cast is None else {"image": None if len(cast) == 0 else (np.array(cast[0], np.float32), np.array(cast[1], np.float32))}
+    oracle.set_state(seed)
+    want = [b["image"] for b in oracle.run_chain(samples, ops, n, {"image": pad}, c_arg)]
+    oracle.set_state(seed)
+    got = chain.run_fused(pkg, ctx, samples, "image", ops, n, cast, pad)
+    g, w = got[0], want[0]
+    assert g.shape == w.shape and g.dtype == w.dtype, (ops, g.shape, w.shape)
+    step = 1.0 if cast is None else (1.0 / 255 if len(cast) == 0 else 1.0 / 255 / min(cast[1]))
+    d = np.abs(g.astype(np.float64) - w.astype(np.float64))
+    assert d.max() <= step * 1.0001, ops
+    assert (d > 0).mean() <= RESIZE_MISMATCH_MAX, ops
