@@ -3,12 +3,14 @@
 // bytes; the result is the image as uint8 [H, W, C], or with `info` the int64
 // pair {width, height}.
 //
-// What this build decodes: binary PNM (P5 grey, P6 colour, maxval <= 255) -
-// the formats whose pixels are the file's bytes.  The reference decodes JPEG
-// with libjpeg-turbo and everything else with stb_image (core/image/ImageIO.cpp,
-// ImageJPEG.cpp, ImageSTBI.cpp); neither library is available here, and other
-// formats are refused by name rather than guessed at.  As in the reference's
-// stb path a grey file stays one channel (ImageSTBI.cpp:14-33).
+// What this build decodes: PNG (core/image/Png.h: every colour type and bit
+// depth, interlaced or not, with the channel policy of the reference's stb
+// path) and binary PNM (P5 grey, P6 colour, maxval <= 255), whose pixels are
+// the file's bytes.  The reference decodes JPEG with libjpeg-turbo and
+// everything else with stb_image (core/image/ImageIO.cpp, ImageJPEG.cpp,
+// ImageSTBI.cpp); neither library is available here, and other formats are
+// refused by name rather than guessed at.  As in the reference's stb path a
+// grey file stays one channel (ImageSTBI.cpp:14-33).
 //
 // The point of the op here is where the pixels land: they are read from the
 // file (or copied from the buffer) straight into a page-locked block of the
@@ -23,6 +25,7 @@
 #include <string>
 #include <vector>
 
+#include "mlx/data/core/image/Png.h"
 #include "mlx/data/gpu/Runtime.h"
 #include "mlx/data/op/KeyTransform.h"
 
@@ -100,6 +103,9 @@ class LoadImage : public KeyTransformOp {
     if (from_memory_) {
       const auto* bytes = static_cast<const unsigned char*>(src->data());
       const size_t size = static_cast<size_t>(src->size()) * src->itemsize();
+      if (core::image::png_signature(bytes, size)) {
+        return png(bytes, size, "stream");
+      }
       Header h;
       if (!parse_header(bytes, size, h)) {
         return refuse("stream");
@@ -126,6 +132,17 @@ class LoadImage : public KeyTransformOp {
     }
     unsigned char head[512];
     const size_t got = std::fread(head, 1, sizeof(head), f);
+    if (core::image::png_signature(head, got)) {
+      // a compressed file is read whole; its pixels are decoded into the page-locked block
+      std::vector<unsigned char> file(head, head + got);
+      unsigned char chunk[1 << 16];
+      size_t n;
+      while ((n = std::fread(chunk, 1, sizeof(chunk), f)) > 0) {
+        file.insert(file.end(), chunk, chunk + n);
+      }
+      std::fclose(f);
+      return png(file.data(), file.size(), path.string());
+    }
     Header h;
     if (!parse_header(head, got, h)) {
       std::fclose(f);
@@ -154,14 +171,29 @@ class LoadImage : public KeyTransformOp {
   }
 
  private:
+  std::shared_ptr<Array> png(const unsigned char* bytes, size_t size, const std::string& what) const {
+    core::image::PngHeader h;
+    std::string why;
+    if (!core::image::png_header(bytes, size, h, why)) {
+      throw std::runtime_error("LoadImage: unable to load image <" + what + "> (" + why + ")");
+    }
+    if (info_) {
+      return std::make_shared<Array>(std::vector<int64_t>{h.width, h.height});
+    }
+    auto out = gpu::Runtime::get().pinned_array(UInt8, {h.height, h.width, h.out_channels});
+    if (!core::image::png_decode(bytes, size, h, static_cast<unsigned char*>(out->data()), why)) {
+      throw std::runtime_error("LoadImage: unable to load image <" + what + "> (" + why + ")");
+    }
+    return out;
+  }
   static std::shared_ptr<Array> landing(const Header& h) {
     return gpu::Runtime::get().pinned_array(UInt8, {h.height, h.width, h.channels});
   }
   [[noreturn]] static std::shared_ptr<Array> refuse(const std::string& what) {
     throw std::runtime_error(
         "LoadImage: unable to load image <" + what +
-        ">: this build reads binary PNM (P5, P6) only - the JPEG and stb_image decoders of mlx-data are not "
-        "available here");
+        ">: this build reads PNG and binary PNM (P5, P6) only - the JPEG and stb_image decoders of mlx-data "
+        "are not available here");
   }
 
   std::string prefix_;

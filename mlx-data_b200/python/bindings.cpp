@@ -15,6 +15,7 @@
 #include "mlx/data/Buffer.h"
 #include "mlx/data/Stream.h"
 #include "mlx/data/core/State.h"
+#include "mlx/data/core/image/Png.h"
 #include "mlx/data/gpu/Runtime.h"
 
 namespace py = pybind11;
@@ -664,6 +665,24 @@ PYBIND11_MODULE(_c, m) {
            py::arg("shape"), py::arg("dtype") = "uint8",
            "A numpy array in page-locked host memory: samples stored in such arrays are copied to the "
            "GPU asynchronously at full PCIe speed.");
+  core.def("png_decode",
+           [](py::bytes file) {
+             const std::string bytes = file;
+             const auto* data = reinterpret_cast<const unsigned char*>(bytes.data());
+             core::image::PngHeader h;
+             std::string why;
+             if (!core::image::png_header(data, bytes.size(), h, why)) {
+               throw std::runtime_error("png_decode: " + why);
+             }
+             py::array_t<uint8_t> out({h.height, h.width, (int64_t)h.out_channels});
+             if (!core::image::png_decode(data, bytes.size(), h, out.mutable_data(), why)) {
+               throw std::runtime_error("png_decode: " + why);
+             }
+             return out;
+           },
+           py::arg("file"),
+           "The pixels load_image produces for a PNG file's bytes, as uint8 [H, W, C] in ordinary memory "
+           "(load_image itself decodes into page-locked memory and needs a GPU).");
   core.def("bind_host_threads_to_node_of",
            [](const std::string& pci_bus_id, const std::string& sysfs) {
              const auto r = gpu::Runtime::bind_host_threads_to_node_of(pci_bus_id, sysfs);

@@ -1,5 +1,5 @@
-"""load_image feeding the fused path: binary PNM files (and in-memory copies)
-are read into page-locked memory, then resized, cropped, batched and cast in
+"""load_image feeding the fused path: binary PNM and PNG files (and in-memory
+copies) are read or decoded into page-locked memory, then resized, cropped, batched and cast in
 one launch per batch; the result must equal the oracle's on the pixel arrays
 the files were written from."""
 import numpy as np
@@ -12,22 +12,27 @@ OPS = [("image_resize_smallest_side", dict(key="image", size=40)),
        ("image_random_h_flip", dict(key="image", prob=0.5))]
 
 
-def _write(path, arr):
+def _write(path, arr, fmt="pnm"):
     h, w = arr.shape[:2]
+    if fmt == "png":
+        from test_png_cpu import write_png
+        path.write_bytes(write_png(arr.astype(np.int64), 8, 2 if arr.shape[2] == 3 else 0, interlace=bool(h % 2)))
+        return
     magic = b"P6" if arr.shape[2] == 3 else b"P5"
     path.write_bytes(magic + b"\n# c\n%d %d\n255\n" % (w, h) + arr.tobytes())
 
 
 @pytest.mark.parametrize("channels", [3, 1])
 @pytest.mark.parametrize("from_memory", [False, True])
-def test_load_then_fused_chain(pkg, oracle, tmp_path, channels, from_memory):
+@pytest.mark.parametrize("fmt", ["pnm", "png"])
+def test_load_then_fused_chain(pkg, oracle, tmp_path, channels, from_memory, fmt):
     rng = np.random.default_rng(5 + channels)
     arrays = [rng.integers(0, 256, (int(rng.integers(50, 90)), int(rng.integers(50, 90)), channels), dtype=np.uint8)
               for _ in range(6)]
     samples = []
     for i, a in enumerate(arrays):
-        name = "im%d.%s" % (i, "ppm" if channels == 3 else "pgm")
-        _write(tmp_path / name, a)
+        name = "im%d.%s" % (i, "png" if fmt == "png" else ("ppm" if channels == 3 else "pgm"))
+        _write(tmp_path / name, a, fmt)
         if from_memory:
             samples.append({"image": np.frombuffer((tmp_path / name).read_bytes(), dtype=np.uint8)})
         else:

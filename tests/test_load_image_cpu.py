@@ -31,10 +31,13 @@ def test_info_from_file_and_memory(pkg, tmp_path):
 
 
 def test_refusals(pkg, tmp_path):
-    (tmp_path / "x.png").write_bytes(b"\x89PNG\r\n\x1a\n" + bytes(64))
+    (tmp_path / "x.gif").write_bytes(b"GIF89a" + bytes(64))
     (tmp_path / "ascii.ppm").write_bytes(b"P3\n1 1\n255\n1 2 3\n")
     (tmp_path / "deep.ppm").write_bytes(b"P6\n1 1\n65535\n" + bytes(6))
-    for name in ("x.png", "ascii.ppm", "deep.ppm"):
+    (tmp_path / "x.png").write_bytes(b"\x89PNG\r\n\x1a\n" + bytes(64))
+    with pytest.raises(RuntimeError, match="IHDR"):
+        pkg.buffer_from_vector([{"file": b"x.png"}]).load_image("file", prefix=str(tmp_path), info=True)[0]
+    for name in ("x.gif", "ascii.ppm", "deep.ppm"):
         with pytest.raises(RuntimeError, match="binary PNM"):
             pkg.buffer_from_vector([{"file": name.encode()}]).load_image("file", prefix=str(tmp_path), info=True)[0]
     with pytest.raises(RuntimeError, match="unable to load image"):
