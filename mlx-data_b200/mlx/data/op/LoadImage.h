@@ -3,14 +3,17 @@
 // bytes; the result is the image as uint8 [H, W, C], or with `info` the int64
 // pair {width, height}.
 //
-// What this build decodes: PNG (core/image/Png.h: every colour type and bit
-// depth, interlaced or not, with the channel policy of the reference's stb
-// path) and binary PNM (P5 grey, P6 colour, maxval <= 255), whose pixels are
-// the file's bytes.  The reference decodes JPEG with libjpeg-turbo and
-// everything else with stb_image (core/image/ImageIO.cpp, ImageJPEG.cpp,
-// ImageSTBI.cpp); neither library is available here, and other formats are
-// refused by name rather than guessed at.  As in the reference's stb path a
-// grey file stays one channel (ImageSTBI.cpp:14-33).
+// What this build decodes: baseline JPEG (core/image/Jpeg.h: the arithmetic
+// of libjpeg-turbo's defaults, always three channels as in
+// core/image/ImageJPEG.cpp:99-146), PNG (core/image/Png.h: every colour type
+// and bit depth, interlaced or not, with the channel policy of the reference's
+// stb path) and binary PNM (P5 grey, P6 colour, maxval <= 255), whose pixels
+// are the file's bytes.  The reference uses libjpeg-turbo and stb_image
+// (core/image/ImageIO.cpp, ImageJPEG.cpp, ImageSTBI.cpp); neither library is
+// available here, so the decoders are this library's own, and what they do
+// not read (progressive and CMYK JPEG, the other stb formats) is refused by
+// name rather than guessed at.  As in the reference's stb path a grey PNG or
+// PNM stays one channel (ImageSTBI.cpp:14-33).
 //
 // The point of the op here is where the pixels land: they are read from the
 // file (or copied from the buffer) straight into a page-locked block of the
@@ -25,6 +28,7 @@
 #include <string>
 #include <vector>
 
+#include "mlx/data/core/image/Jpeg.h"
 #include "mlx/data/core/image/Png.h"
 #include "mlx/data/gpu/Runtime.h"
 #include "mlx/data/op/KeyTransform.h"
@@ -106,6 +110,9 @@ class LoadImage : public KeyTransformOp {
       if (core::image::png_signature(bytes, size)) {
         return png(bytes, size, "stream");
       }
+      if (core::image::jpeg_signature(bytes, size)) {
+        return jpeg(bytes, size, "stream");
+      }
       Header h;
       if (!parse_header(bytes, size, h)) {
         return refuse("stream");
@@ -132,7 +139,7 @@ class LoadImage : public KeyTransformOp {
     }
     unsigned char head[512];
     const size_t got = std::fread(head, 1, sizeof(head), f);
-    if (core::image::png_signature(head, got)) {
+    if (core::image::png_signature(head, got) || core::image::jpeg_signature(head, got)) {
       // a compressed file is read whole; its pixels are decoded into the page-locked block
       std::vector<unsigned char> file(head, head + got);
       unsigned char chunk[1 << 16];
@@ -141,7 +148,8 @@ class LoadImage : public KeyTransformOp {
         file.insert(file.end(), chunk, chunk + n);
       }
       std::fclose(f);
-      return png(file.data(), file.size(), path.string());
+      return core::image::png_signature(head, got) ? png(file.data(), file.size(), path.string())
+                                                   : jpeg(file.data(), file.size(), path.string());
     }
     Header h;
     if (!parse_header(head, got, h)) {
@@ -186,14 +194,29 @@ class LoadImage : public KeyTransformOp {
     }
     return out;
   }
+  std::shared_ptr<Array> jpeg(const unsigned char* bytes, size_t size, const std::string& what) const {
+    core::image::JpegHeader h;
+    std::string why;
+    if (!core::image::jpeg_header(bytes, size, h, why)) {
+      throw std::runtime_error("LoadImage: unable to load image <" + what + "> (" + why + ")");
+    }
+    if (info_) {
+      return std::make_shared<Array>(std::vector<int64_t>{h.width, h.height});
+    }
+    auto out = gpu::Runtime::get().pinned_array(UInt8, {h.height, h.width, 3});
+    if (!core::image::jpeg_decode(bytes, size, static_cast<unsigned char*>(out->data()), why)) {
+      throw std::runtime_error("LoadImage: unable to load image <" + what + "> (" + why + ")");
+    }
+    return out;
+  }
   static std::shared_ptr<Array> landing(const Header& h) {
     return gpu::Runtime::get().pinned_array(UInt8, {h.height, h.width, h.channels});
   }
   [[noreturn]] static std::shared_ptr<Array> refuse(const std::string& what) {
     throw std::runtime_error(
         "LoadImage: unable to load image <" + what +
-        ">: this build reads PNG and binary PNM (P5, P6) only - the JPEG and stb_image decoders of mlx-data "
-        "are not available here");
+        ">: this build reads baseline JPEG, PNG and binary PNM (P5, P6) - libjpeg-turbo and stb_image, which "
+        "mlx-data decodes with, are not available here");
   }
 
   std::string prefix_;

@@ -15,6 +15,7 @@
 #include "mlx/data/Buffer.h"
 #include "mlx/data/Stream.h"
 #include "mlx/data/core/State.h"
+#include "mlx/data/core/image/Jpeg.h"
 #include "mlx/data/core/image/Png.h"
 #include "mlx/data/gpu/Runtime.h"
 
@@ -665,6 +666,24 @@ PYBIND11_MODULE(_c, m) {
            py::arg("shape"), py::arg("dtype") = "uint8",
            "A numpy array in page-locked host memory: samples stored in such arrays are copied to the "
            "GPU asynchronously at full PCIe speed.");
+  core.def("jpeg_decode",
+           [](py::bytes file) {
+             const std::string bytes = file;
+             const auto* data = reinterpret_cast<const unsigned char*>(bytes.data());
+             core::image::JpegHeader h;
+             std::string why;
+             if (!core::image::jpeg_header(data, bytes.size(), h, why)) {
+               throw std::runtime_error("jpeg_decode: " + why);
+             }
+             py::array_t<uint8_t> out({h.height, h.width, (int64_t)3});
+             if (!core::image::jpeg_decode(data, bytes.size(), out.mutable_data(), why)) {
+               throw std::runtime_error("jpeg_decode: " + why);
+             }
+             return out;
+           },
+           py::arg("file"),
+           "The pixels load_image produces for a baseline JPEG file's bytes, as uint8 [H, W, 3] in ordinary "
+           "memory (load_image itself decodes into page-locked memory and needs a GPU).");
   core.def("png_decode",
            [](py::bytes file) {
              const std::string bytes = file;
