@@ -48,6 +48,7 @@ struct Component {
   int64_t dw = 0, dh = 0;    // true size of the (possibly subsampled) plane
   int pred = 0;
   std::vector<unsigned char> plane;   // [blocks_h * 8][blocks_w * 8]
+  std::vector<int> coef;              // progressive frames: [blocks_h * blocks_w][64], kept across scans
 };
 
 // Entropy-coded segment reader: bytes with FF 00 unstuffed; a marker ends the
@@ -199,6 +200,9 @@ struct Decoder {
   bool saw_jfif = false, saw_adobe = false;
   int adobe_transform = 0;
   bool have_frame = false;
+  bool progressive = false;
+  int ss = 0, se = 63, ah = 0, al = 0;   // spectral band and bit position of the current scan
+  int eobrun = 0;                        // blocks still covered by an end-of-band run
 
   bool fail(const std::string& w) {
     why = w;
@@ -293,12 +297,136 @@ struct Decoder {
       c.dw = (width * c.h + hmax - 1) / hmax;
       c.dh = (height * c.v + vmax - 1) / vmax;
       c.plane.assign(static_cast<size_t>(c.blocks_w) * 8 * c.blocks_h * 8, 0);
+      if (progressive) {
+        c.coef.assign(static_cast<size_t>(c.blocks_w) * c.blocks_h * 64, 0);
+      }
     }
     have_frame = true;
     return true;
   }
 
+  // One block of a progressive scan (T.81 annex G): the scan carries either the
+  // DC terms or one band of AC terms, either their high bits (first pass, value
+  // shifted left by al) or one more bit each (refinement).
+  bool progressive_block(Bits& b, Component& c) {
+    if (bx >= c.blocks_w || by >= c.blocks_h) {
+      return fail("corrupt entropy-coded data");
+    }
+    int* coef = c.coef.data() + (static_cast<size_t>(by) * c.blocks_w + bx) * 64;
+    if (ss == 0) {
+      if (ah == 0) {
+        const int t = decode_symbol(b, dc[c.td]);
+        if (t < 0 || t > 11) {
+          return fail("corrupt entropy-coded data");
+        }
+        c.pred += t ? extend(b.get(t), t) : 0;
+        coef[0] = c.pred * (1 << al);
+      } else if (b.get(1)) {
+        coef[0] |= 1 << al;
+      }
+      return true;
+    }
+    const int p1 = 1 << al, m1 = -(1 << al);
+    int k = ss;
+    if (ah == 0) {
+      if (eobrun > 0) {
+        eobrun--;
+        return true;
+      }
+      while (k <= se) {
+        const int rs = decode_symbol(b, ac[c.ta]);
+        if (rs < 0) {
+          return fail("corrupt entropy-coded data");
+        }
+        const int r = rs >> 4, s = rs & 15;
+        if (s == 0) {
+          if (r < 15) {
+            eobrun = (1 << r) - 1;
+            if (r) {
+              eobrun += b.get(r);
+            }
+            break;
+          }
+          k += 16;
+          continue;
+        }
+        k += r;
+        if (k > se) {
+          return fail("corrupt entropy-coded data");
+        }
+        coef[kZigzag[k]] = extend(b.get(s), s) * (1 << al);
+        k++;
+      }
+      return true;
+    }
+    // refinement of a band: known non-zero terms get one more bit each, new terms are +-1 << al
+    auto refine = [&](int& v) {
+      if (b.get(1) && (v & p1) == 0) {
+        v += v >= 0 ? p1 : m1;
+      }
+    };
+    if (eobrun == 0) {
+      for (; k <= se; k++) {
+        const int rs = decode_symbol(b, ac[c.ta]);
+        if (rs < 0) {
+          return fail("corrupt entropy-coded data");
+        }
+        int r = rs >> 4;
+        const int s = rs & 15;
+        int value = 0;
+        if (s) {
+          value = b.get(1) ? p1 : m1;
+        } else if (r != 15) {
+          eobrun = 1 << r;
+          if (r) {
+            eobrun += b.get(r);
+          }
+          break;
+        }
+        while (k <= se) {
+          int& v = coef[kZigzag[k]];
+          if (v != 0) {
+            refine(v);
+          } else if (--r < 0) {
+            break;
+          }
+          k++;
+        }
+        if (s && k <= se) {
+          coef[kZigzag[k]] = value;
+        }
+      }
+    }
+    if (eobrun > 0) {
+      for (; k <= se; k++) {
+        int& v = coef[kZigzag[k]];
+        if (v != 0) {
+          refine(v);
+        }
+      }
+      eobrun--;
+    }
+    return true;
+  }
+
+  // After the last scan of a progressive frame: every block through the inverse DCT.
+  void finish_progressive() {
+    for (int i = 0; i < ncomp; i++) {
+      Component& c = comp[i];
+      const size_t pitch = static_cast<size_t>(c.blocks_w) * 8;
+      for (int y = 0; y < c.blocks_h; y++) {
+        for (int x = 0; x < c.blocks_w; x++) {
+          idct_block(c.coef.data() + (static_cast<size_t>(y) * c.blocks_w + x) * 64, qt[c.tq],
+                     c.plane.data() + static_cast<size_t>(y) * 8 * pitch + static_cast<size_t>(x) * 8, pitch);
+        }
+      }
+    }
+  }
+
   bool decode_block(Bits& b, Component& c) {
+    if (progressive) {
+      return progressive_block(b, c);
+    }
     int coef[64] = {0};
     const int t = decode_symbol(b, dc[c.td]);
     if (t < 0 || t > 11) {
@@ -360,11 +488,26 @@ struct Decoder {
       }
       sc[i]->td = tables >> 4;
       sc[i]->ta = tables & 15;
-      if (sc[i]->td > 3 || sc[i]->ta > 3 || !dc[sc[i]->td].present || !ac[sc[i]->ta].present ||
-          !qt_present[sc[i]->tq]) {
+      sc[i]->pred = 0;
+    }
+    ss = data[at + 1 + 2 * ns];
+    se = data[at + 2 + 2 * ns];
+    ah = data[at + 3 + 2 * ns] >> 4;
+    al = data[at + 3 + 2 * ns] & 15;
+    eobrun = 0;
+    if (!progressive) {
+      ss = 0;
+      se = 63;
+      ah = al = 0;
+    } else if (ss > se || se > 63 || al > 13 || (ss == 0 && se != 0) || (ss > 0 && ns != 1)) {
+      return fail("bad progressive scan header");
+    }
+    for (int i = 0; i < ns; i++) {
+      const bool needs_dc = ss == 0 && ah == 0, needs_ac = !progressive || ss > 0;
+      if (sc[i]->td > 3 || sc[i]->ta > 3 || (needs_dc && !dc[sc[i]->td].present) ||
+          (needs_ac && !ac[sc[i]->ta].present) || !qt_present[sc[i]->tq]) {
         return fail("scan uses a table the file does not define");
       }
-      sc[i]->pred = 0;
     }
     Bits b{data, size, end};
     int64_t units_x, units_y;
@@ -395,6 +538,7 @@ struct Decoder {
           for (int i = 0; i < ns; i++) {
             sc[i]->pred = 0;
           }
+          eobrun = 0;
         }
         if (ns == 1) {
           bx = static_cast<int>(mx);
@@ -462,6 +606,8 @@ struct Decoder {
       switch (m) {
         case 0xc0:
         case 0xc1:
+        case 0xc2:
+          progressive = m == 0xc2;
           if (have_frame) {
             return fail("more than one frame header");
           }
@@ -472,8 +618,6 @@ struct Decoder {
             return true;
           }
           break;
-        case 0xc2:
-          return fail("progressive JPEG files are not read");
         case 0xc3: case 0xc5: case 0xc6: case 0xc7: case 0xc9: case 0xca: case 0xcb: case 0xcd: case 0xce: case 0xcf:
           return fail("lossless, hierarchical and arithmetic-coded JPEG files are not read");
         case 0xc4:
@@ -521,6 +665,9 @@ struct Decoder {
     }
     if (!header_only && scans == 0) {
       return fail("no image data");
+    }
+    if (!header_only && progressive) {
+      finish_progressive();
     }
     return true;
   }

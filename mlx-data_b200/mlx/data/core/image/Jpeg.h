@@ -1,6 +1,6 @@
-// Baseline JPEG decoding for load_image, written from the JPEG standard (ITU
-// T.81: markers, Huffman-coded sequential DCT scans, restart intervals) and the
-// JFIF colour convention.
+// JPEG decoding for load_image, written from the JPEG standard (ITU T.81:
+// markers, Huffman-coded sequential and progressive DCT scans, restart
+// intervals) and the JFIF colour convention.
 //
 // The reference decodes JPEG with libjpeg-turbo at its default settings
 // (core/image/ImageJPEG.cpp:99-146): the accurate integer inverse DCT, "fancy"
@@ -13,11 +13,13 @@
 // the same integers; tests/test_jpeg_cpu.py holds it to Pillow's decoder,
 // which is libjpeg-turbo with the same defaults.
 //
-// Read here: 8-bit baseline and extended-sequential Huffman files (SOF0, SOF1)
-// with one component (grey) or three (YCbCr, or RGB when an Adobe marker says
-// so), luma sampled 1x1, 2x1, 1x2 or 2x2 against 1x1 chroma, interleaved or
-// not, with or without restart markers.  Progressive, arithmetic-coded,
-// lossless, 12-bit and four-component (CMYK) files are refused by name.
+// Read here: 8-bit baseline, extended-sequential and progressive Huffman files
+// (SOF0, SOF1, SOF2) with one component (grey) or three (YCbCr, or RGB when an
+// Adobe marker says so), luma sampled 1x1, 2x1, 1x2 or 2x2 against 1x1 chroma,
+// interleaved or not, with or without restart markers.  A progressive file is
+// decoded from all its scans (spectral selection and successive
+// approximation), then transformed once.  Arithmetic-coded, lossless, 12-bit
+// and four-component (CMYK) files are refused by name.
 #pragma once
 
 #include <cstddef>

@@ -3,7 +3,7 @@
 // bytes; the result is the image as uint8 [H, W, C], or with `info` the int64
 // pair {width, height}.
 //
-// What this build decodes: baseline JPEG (core/image/Jpeg.h: the arithmetic
+// What this build decodes: JPEG, baseline and progressive (core/image/Jpeg.h: the arithmetic
 // of libjpeg-turbo's defaults, always three channels as in
 // core/image/ImageJPEG.cpp:99-146), PNG (core/image/Png.h: every colour type
 // and bit depth, interlaced or not, with the channel policy of the reference's
@@ -11,7 +11,7 @@
 // are the file's bytes.  The reference uses libjpeg-turbo and stb_image
 // (core/image/ImageIO.cpp, ImageJPEG.cpp, ImageSTBI.cpp); neither library is
 // available here, so the decoders are this library's own, and what they do
-// not read (progressive and CMYK JPEG, the other stb formats) is refused by
+// not read (CMYK and arithmetic-coded JPEG, the other stb formats) is refused by
 // name rather than guessed at.  As in the reference's stb path a grey PNG or
 // PNM stays one channel (ImageSTBI.cpp:14-33).
 //
@@ -215,7 +215,7 @@ class LoadImage : public KeyTransformOp {
   [[noreturn]] static std::shared_ptr<Array> refuse(const std::string& what) {
     throw std::runtime_error(
         "LoadImage: unable to load image <" + what +
-        ">: this build reads baseline JPEG, PNG and binary PNM (P5, P6) - libjpeg-turbo and stb_image, which "
+        ">: this build reads JPEG, PNG and binary PNM (P5, P6) - libjpeg-turbo and stb_image, which "
         "mlx-data decodes with, are not available here");
   }
 

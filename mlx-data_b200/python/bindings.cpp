@@ -682,7 +682,7 @@ PYBIND11_MODULE(_c, m) {
              return out;
            },
            py::arg("file"),
-           "The pixels load_image produces for a baseline JPEG file's bytes, as uint8 [H, W, 3] in ordinary "
+           "The pixels load_image produces for a JPEG file's bytes, as uint8 [H, W, 3] in ordinary "
            "memory (load_image itself decodes into page-locked memory and needs a GPU).");
   core.def("png_decode",
            [](py::bytes file) {

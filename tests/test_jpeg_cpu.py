@@ -1,4 +1,4 @@
-"""The baseline JPEG decoder behind load_image, on the CPU, against Pillow's
+"""The JPEG decoder (baseline and progressive) behind load_image, on the CPU, against Pillow's
 decoder - libjpeg-turbo at its defaults, which is what the reference calls
 (mlx/data/core/image/ImageJPEG.cpp:99-146): accurate integer IDCT, triangle
 chroma upsampling, fixed-point YCbCr -> RGB, grey copied to three channels.
@@ -9,6 +9,9 @@ import numpy as np
 import pytest
 
 Image = pytest.importorskip("PIL.Image")
+from PIL import ImageFile  # noqa: E402
+
+ImageFile.MAXBLOCK = 1 << 22   # Pillow's encoder wants the whole progressive file in one buffer
 
 
 def _enc(img, **kw):
@@ -34,11 +37,14 @@ SIZES = [(1, 1), (2, 3), (7, 9), (8, 8), (16, 16), (17, 33), (33, 17), (64, 48),
 
 @pytest.mark.parametrize("subsampling", [0, 1, 2])
 @pytest.mark.parametrize("quality", [10, 50, 90, 100])
-def test_colour_files(pkg, subsampling, quality):
+@pytest.mark.parametrize("progressive", [False, True])
+def test_colour_files(pkg, subsampling, quality, progressive):
     rng = np.random.default_rng(subsampling * 10 + quality)
     for h, w in SIZES:
         for noise in (4, 60):
-            file = _enc(Image.fromarray(_picture(rng, h, w, 3, noise), "RGB"), quality=quality, subsampling=subsampling)
+            file = _enc(Image.fromarray(_picture(rng, h, w, 3, noise), "RGB"), quality=quality, subsampling=subsampling,
+                        progressive=progressive, optimize=progressive and noise == 60)
+            assert (b"\xff\xc2" in file) == progressive
             got = pkg.core.jpeg_decode(file)
             want = _pillow(file)
             assert got.shape == want.shape == (h, w, 3)
@@ -47,8 +53,8 @@ def test_colour_files(pkg, subsampling, quality):
 
 def test_grey_files_come_back_with_three_channels(pkg):
     rng = np.random.default_rng(3)
-    for h, w in SIZES:
-        file = _enc(Image.fromarray(_picture(rng, h, w, 1, 30), "L"), quality=80)
+    for i, (h, w) in enumerate(SIZES):
+        file = _enc(Image.fromarray(_picture(rng, h, w, 1, 30), "L"), quality=80, progressive=bool(i % 2))
         got = pkg.core.jpeg_decode(file)
         assert got.shape == (h, w, 3)
         assert np.array_equal(got, _pillow(file))
@@ -59,7 +65,8 @@ def test_optimised_tables_and_restart_markers(pkg):
     rng = np.random.default_rng(4)
     a = Image.fromarray(_picture(rng, 150, 203, 3, 25), "RGB")
     for kw in (dict(optimize=True), dict(restart_marker_blocks=3), dict(restart_marker_rows=1, subsampling=0),
-               dict(optimize=True, restart_marker_blocks=1, subsampling=1)):
+               dict(optimize=True, restart_marker_blocks=1, subsampling=1),
+               dict(progressive=True, restart_marker_blocks=2), dict(progressive=True, restart_marker_rows=1, subsampling=1)):
         file = _enc(a, quality=70, **kw)
         assert np.array_equal(pkg.core.jpeg_decode(file), _pillow(file)), kw
     # the restart markers are really there
@@ -69,8 +76,6 @@ def test_optimised_tables_and_restart_markers(pkg):
 def test_what_is_not_read_is_refused_by_name(pkg):
     rng = np.random.default_rng(6)
     a = Image.fromarray(_picture(rng, 40, 40, 3, 10), "RGB")
-    with pytest.raises(RuntimeError, match="progressive"):
-        pkg.core.jpeg_decode(_enc(a, progressive=True))
     with pytest.raises(RuntimeError, match="CMYK"):
         pkg.core.jpeg_decode(_enc(a.convert("CMYK")))
     good = _enc(a)
