@@ -130,8 +130,8 @@ inline void idct_1d(const int64_t in[8], int64_t out[8], int shift) {
   int64_t z1 = (z2 + z3) * F0_541;
   const int64_t tmp2 = z1 - z3 * F1_847;
   const int64_t tmp3 = z1 + z2 * F0_765;
-  const int64_t tmp0 = (in[0] + in[4]) << kConstBits;
-  const int64_t tmp1 = (in[0] - in[4]) << kConstBits;
+  const int64_t tmp0 = (in[0] + in[4]) * (int64_t(1) << kConstBits);
+  const int64_t tmp1 = (in[0] - in[4]) * (int64_t(1) << kConstBits);
   const int64_t tmp10 = tmp0 + tmp3, tmp13 = tmp0 - tmp3, tmp11 = tmp1 + tmp2, tmp12 = tmp1 - tmp2;
   // odd part
   int64_t t0 = in[7], t1 = in[5], t2 = in[3], t3 = in[1];
