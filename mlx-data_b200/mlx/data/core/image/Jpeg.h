@@ -19,7 +19,9 @@
 // interleaved or not, with or without restart markers.  A progressive file is
 // decoded from all its scans (spectral selection and successive
 // approximation), then transformed once.  Arithmetic-coded, lossless, 12-bit
-// and four-component (CMYK) files are refused by name.
+// and four-component (CMYK) files are refused by name.  Luma sampled 1x2
+// ("4:4:0") is filtered vertically by the same 3:1 rule; Pillow writes no such
+// file, so that one case is not pinned.
 #pragma once
 
 #include <cstddef>
