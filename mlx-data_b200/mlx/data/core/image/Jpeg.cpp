@@ -19,6 +19,9 @@ struct Huffman {
   bool present = false;
   unsigned char values[256];
   int mincode[17], maxcode[18], valptr[17];
+  // codes of at most kLook bits, by their first kLook bits: length << 8 | value, 0 for longer codes
+  static constexpr int kLook = 9;
+  uint16_t look[1 << kLook];
 
   // bits[l] = number of codes of length l (1..16), values in code order
   bool build(const unsigned char* bits, const unsigned char* vals, int count) {
@@ -36,6 +39,16 @@ struct Huffman {
       code <<= 1;
     }
     maxcode[17] = 0x7fffffff;
+    std::memset(look, 0, sizeof(look));
+    for (int l = 1; l <= kLook; l++) {
+      for (int i = 0; i < bits[l]; i++) {
+        const int c = mincode[l] + i;
+        const int first = c << (kLook - l);
+        for (int fill = 0; fill < (1 << (kLook - l)); fill++) {
+          look[first + fill] = static_cast<uint16_t>(l << 8 | values[valptr[l] + i]);
+        }
+      }
+    }
     present = true;
     return true;
   }
@@ -93,6 +106,16 @@ struct Bits {
     count -= n;
     return v;
   }
+  int peek(int n) {
+    if (count < n) {
+      fill();
+    }
+    return static_cast<int>(acc >> (32 - n));
+  }
+  void skip(int n) {
+    acc <<= n;
+    count -= n;
+  }
   void restart() {
     acc = 0;
     count = 0;
@@ -101,8 +124,13 @@ struct Bits {
 };
 
 int decode_symbol(Bits& b, const Huffman& t) {
-  int code = 0;
-  for (int l = 1; l <= 16; l++) {
+  const unsigned hit = t.look[b.peek(Huffman::kLook)];
+  if (hit) {
+    b.skip(hit >> 8);
+    return hit & 0xff;
+  }
+  int code = b.get(Huffman::kLook);
+  for (int l = Huffman::kLook + 1; l <= 16; l++) {
     code = (code << 1) | b.get(1);
     if (t.maxcode[l] >= 0 && code <= t.maxcode[l] && code >= t.mincode[l]) {
       return t.values[t.valptr[l] + code - t.mincode[l]];
@@ -166,6 +194,14 @@ void idct_block(const int coef[64], const uint16_t* q, unsigned char* dst, size_
   int64_t ws[64];
   for (int c = 0; c < 8; c++) {
     int64_t in[8], out[8];
+    if ((coef[8 + c] | coef[16 + c] | coef[24 + c] | coef[32 + c] | coef[40 + c] | coef[48 + c] | coef[56 + c]) == 0) {
+      // a column with only its DC term: the transform of a constant, exactly dc * 4 after the first descaling
+      const int64_t dcv = static_cast<int64_t>(coef[c]) * q[c] * (1 << kPass1Bits);
+      for (int r = 0; r < 8; r++) {
+        ws[r * 8 + c] = dcv;
+      }
+      continue;
+    }
     for (int r = 0; r < 8; r++) {
       in[r] = static_cast<int64_t>(coef[r * 8 + c]) * q[r * 8 + c];
     }
