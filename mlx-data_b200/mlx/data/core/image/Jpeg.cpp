@@ -227,7 +227,7 @@ struct Decoder {
   uint16_t qt[4][64];
   bool qt_present[4] = {false, false, false, false};
   Huffman dc[4], ac[4];
-  Component comp[3];
+  Component comp[4];
   int ncomp = 0;
   int64_t width = 0, height = 0;
   int hmax = 1, vmax = 1;
@@ -297,10 +297,7 @@ struct Decoder {
     if (width <= 0 || height <= 0) {
       return fail("image size missing from the frame header");
     }
-    if (ncomp == 4) {
-      return fail("four-component (CMYK) JPEG files are not read");
-    }
-    if ((ncomp != 1 && ncomp != 3) || end - at < static_cast<size_t>(6 + 3 * ncomp)) {
+    if ((ncomp != 1 && ncomp != 3 && ncomp != 4) || end - at < static_cast<size_t>(6 + 3 * ncomp)) {
       return fail("bad frame header");
     }
     hmax = vmax = 1;
@@ -510,7 +507,7 @@ struct Decoder {
     if (ns < 1 || ns > ncomp || end - at < static_cast<size_t>(1 + 2 * ns + 3)) {
       return fail("bad scan header");
     }
-    Component* sc[3];
+    Component* sc[4];
     for (int i = 0; i < ns; i++) {
       const int id = data[at + 1 + 2 * i], tables = data[at + 2 + 2 * i];
       sc[i] = nullptr;
@@ -708,6 +705,12 @@ struct Decoder {
     return true;
   }
 
+  // Four components: CMYK as stored, or - when the Adobe marker says so - YCCK,
+  // whose first three are converted like YCbCr and then inverted.
+  bool is_ycck() const {
+    return ncomp == 4 && saw_adobe && adobe_transform == 2;
+  }
+
   bool is_rgb() const {
     if (ncomp != 3) {
       return false;
@@ -839,7 +842,9 @@ bool jpeg_decode(const unsigned char* data, size_t size, unsigned char* out, std
     cr_g[i] = -46802 * x;                    // 0.71414
     cb_g[i] = -22554 * x + 32768;            // 0.34414
   }
-  const bool rgb = d.is_rgb();
+  // four components: the reference keeps the first three of libjpeg's CMYK output
+  const bool rgb = d.is_rgb() || (d.ncomp == 4 && !d.is_ycck());
+  const bool invert = d.is_ycck();
   std::vector<unsigned char> rows[3];
   std::vector<int> tmp;
   for (int i = 0; i < 3; i++) {
@@ -864,6 +869,11 @@ bool jpeg_decode(const unsigned char* data, size_t size, unsigned char* out, std
         o[3 * x] = clamp8(yy + cr_r[cr]);
         o[3 * x + 1] = clamp8(yy + ((cb_g[cb] + cr_g[cr]) >> 16));
         o[3 * x + 2] = clamp8(yy + cb_b[cb]);
+      }
+      if (invert) {
+        for (int64_t x = 0; x < 3 * w; x++) {
+          o[x] = static_cast<unsigned char>(255 - o[x]);
+        }
       }
     }
   }

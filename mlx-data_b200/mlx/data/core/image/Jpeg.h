@@ -18,8 +18,10 @@
 // Adobe marker says so), luma sampled 1x1, 2x1, 1x2 or 2x2 against 1x1 chroma,
 // interleaved or not, with or without restart markers.  A progressive file is
 // decoded from all its scans (spectral selection and successive
-// approximation), then transformed once.  Arithmetic-coded, lossless, 12-bit
-// and four-component (CMYK) files are refused by name.  Luma sampled 1x2
+// approximation), then transformed once.  Four-component files give the first
+// three channels of libjpeg's CMYK output, as the reference keeps them: the
+// stored C, M, Y, or for Adobe YCCK files the converted and inverted ones.
+// Arithmetic-coded, lossless and 12-bit files are refused by name.  Luma sampled 1x2
 // ("4:4:0") is filtered vertically by the same 3:1 rule; Pillow writes no such
 // file, so that one case is not pinned.
 #pragma once
@@ -35,7 +37,7 @@ namespace image {
 
 struct JpegHeader {
   int64_t width = 0, height = 0;
-  int components = 0;   // in the file: 1 or 3
+  int components = 0;   // in the file: 1, 3 or 4
 };
 
 // True when the bytes start with the JPEG signature (FF D8 FF).

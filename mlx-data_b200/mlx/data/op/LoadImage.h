@@ -11,7 +11,7 @@
 // are the file's bytes.  The reference uses libjpeg-turbo and stb_image
 // (core/image/ImageIO.cpp, ImageJPEG.cpp, ImageSTBI.cpp); neither library is
 // available here, so the decoders are this library's own, and what they do
-// not read (CMYK and arithmetic-coded JPEG, the other stb formats) is refused by
+// not read (arithmetic-coded and 12-bit JPEG, the other stb formats) is refused by
 // name rather than guessed at.  As in the reference's stb path a grey PNG or
 // PNM stays one channel (ImageSTBI.cpp:14-33).
 //

@@ -73,11 +73,24 @@ def test_optimised_tables_and_restart_markers(pkg):
     assert b"\xff\xd0" in _enc(a, quality=70, restart_marker_blocks=3)
 
 
+def test_four_component_files_keep_their_first_three_channels(pkg):
+    """libjpeg hands such a file out as CMYK and the reference keeps channels
+    0-2 of that.  Pillow shows CMYK files inverted (the Adobe convention), so
+    libjpeg's own samples are 255 minus Pillow's."""
+    rng = np.random.default_rng(9)
+    for h, w in SIZES:
+        for kw in (dict(), dict(subsampling=2, progressive=True), dict(quality=30, subsampling=1)):
+            a = np.stack([_picture(rng, h, w, 1, 15) for _ in range(4)], axis=-1)
+            file = _enc(Image.fromarray(a, "CMYK"), **kw)
+            im = Image.open(io.BytesIO(file))
+            assert im.mode == "CMYK"
+            got = pkg.core.jpeg_decode(file)
+            assert np.array_equal(got, 255 - np.asarray(im)[..., :3]), (h, w, kw)
+
+
 def test_what_is_not_read_is_refused_by_name(pkg):
     rng = np.random.default_rng(6)
     a = Image.fromarray(_picture(rng, 40, 40, 3, 10), "RGB")
-    with pytest.raises(RuntimeError, match="CMYK"):
-        pkg.core.jpeg_decode(_enc(a.convert("CMYK")))
     good = _enc(a)
     with pytest.raises(RuntimeError, match="JPEG"):
         pkg.core.jpeg_decode(b"\x00" + good)
