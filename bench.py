@@ -143,6 +143,46 @@ def build_pipeline(dx, samples, ops, batch, cast, native=True, prefetch=None):
     return ds
 
 
+def jpeg_fed_rate(dx, shapes, ops, batch, cast, lanes):
+    """The chain fed from JPEG files held in memory: load_image (this package's
+    decoder, one file per worker thread at a time) -> image ops -> batch -> cast,
+    host float32 batches out.  Files: photographs are smooth, so the synthetic
+    ones are coarse random colour fields with mild noise, 4:2:0, quality 90."""
+    import io
+    import torch
+    from PIL import Image
+    rng = np.random.default_rng(7)
+    files = []
+    for h, w in shapes[:16]:
+        coarse = rng.integers(0, 256, (h // 16 + 2, w // 16 + 2, 3)).astype(np.float32)
+        img = np.kron(coarse, np.ones((16, 16, 1), np.float32))[:h, :w] + rng.normal(0, 6, (h, w, 3))
+        buf = io.BytesIO()
+        Image.fromarray(np.clip(img, 0, 255).astype(np.uint8)).save(buf, format="JPEG", quality=90, subsampling=2)
+        files.append(np.frombuffer(buf.getvalue(), dtype=np.uint8))
+    threads = len(os.sched_getaffinity(0))
+    n_batches = max(3, (1024 + batch - 1) // batch)
+    samples = [{"image": files[i % len(files)]} for i in range(batch * n_batches)]
+
+    def pipeline(some):
+        ds = dx.buffer_from_vector(some).to_stream().load_image("image", from_memory=True).prefetch(threads, threads)
+        for name, kw in ops:
+            ds = getattr(ds, name)(**dict(kw))
+        return ds.batch(batch).key_cast("image", **cast_kwargs(cast)).prefetch(lanes, lanes)
+
+    for _ in pipeline(samples[:batch]):      # warm-up: staging pools, decoder code
+        pass
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n_img = 0
+    for bb in pipeline(samples):
+        n_img += bb["image"].shape[0]
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    return {"value": n_img / dt, "unit": "images/s", "decode_threads": threads, "images": n_img,
+            "mean_file_bytes": int(np.mean([f.size for f in files])),
+            "decoder": "this package's (scalar, pixel-equal to libjpeg-turbo's defaults)"}
+
+
 def pool_shapes(wl, name, count):
     _, hs, ws = wl.image_sizes(name, "full", n=count)
     return [(int(h), int(w)) for h, w in zip(hs, ws)]
@@ -353,6 +393,8 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of one batch with the CPU oracle")
     ap.add_argument("--host-affinity", default="auto", choices=["auto", "on", "off"],
                     help="keep each rank's host threads on its GPU's NUMA node (auto: when more than one rank runs)")
+    ap.add_argument("--from-jpeg", action="store_true",
+                    help="add e2e.from_jpeg: the chain fed from JPEG files in memory through load_image (needs Pillow to write them)")
     ap.add_argument("--repeats", type=int, default=0, help="times the K steps are repeated inside the timed region (0: about one second)")
     args = ap.parse_args()
     wl = load_workloads()
@@ -550,6 +592,8 @@ def main():
             e2e["pageable"] = run_host_leg(plain_pool, max(4, Ke // 2), False)
             e2e["pageable"]["host_memory"] = "ordinary numpy arrays, packed into page-locked blocks by the calling thread"
         dx.core.set_device_output(False)
+        if args.from_jpeg and world == 1:
+            e2e["from_jpeg"] = jpeg_fed_rate(dx, shapes, ops, batch, cfg["cast"], lanes)
         if world > 1:
             # What the host side can move at all: every rank copies page-locked
             # blocks to and from its GPU at the same time, nothing else running.
