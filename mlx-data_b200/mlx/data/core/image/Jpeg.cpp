@@ -212,7 +212,15 @@ void idct_block(const int coef[64], const uint16_t* q, unsigned char* dst, size_
   }
   for (int r = 0; r < 8; r++) {
     int64_t out[8];
-    idct_1d(ws + r * 8, out, kConstBits + kPass1Bits + 3);
+    const int64_t* w = ws + r * 8;
+    if ((w[1] | w[2] | w[3] | w[4] | w[5] | w[6] | w[7]) == 0) {
+      // a row with only its first term is constant: the same value the full transform gives
+      int64_t v = descale(w[0] * (int64_t(1) << kConstBits), kConstBits + kPass1Bits + 3) + 128;
+      v = v < 0 ? 0 : (v > 255 ? 255 : v);
+      std::memset(dst + r * pitch, static_cast<int>(v), 8);
+      continue;
+    }
+    idct_1d(w, out, kConstBits + kPass1Bits + 3);
     for (int c = 0; c < 8; c++) {
       const int64_t v = out[c] + 128;
       dst[r * pitch + c] = static_cast<unsigned char>(v < 0 ? 0 : (v > 255 ? 255 : v));
