@@ -69,13 +69,31 @@ struct Component {
 struct Bits {
   const unsigned char* data;
   size_t size, pos;
-  uint32_t acc = 0;
+  uint64_t acc = 0;   // the next bits, left-aligned; the top `count` of them are valid
   int count = 0;
   bool hit_marker = false;
 
   void fill() {
-    while (count <= 24) {
-      unsigned b = 0;
+    // eight bytes at once when none of them is FF (no stuffing, no marker)
+    if (!hit_marker && pos + 8 <= size) {
+      uint64_t v = 0;
+      for (int i = 0; i < 8; i++) {
+        v = v << 8 | data[pos + i];
+      }
+      const uint64_t x = ~v;
+      if (((x - 0x0101010101010101ULL) & ~x & 0x8080808080808080ULL) == 0) {
+        const int bytes = (64 - count) >> 3;
+        if (bytes > 0) {
+          const uint64_t chunk = bytes == 8 ? v : v & ~((uint64_t(1) << (64 - 8 * bytes)) - 1);
+          acc |= chunk >> count;
+          count += 8 * bytes;
+          pos += bytes;
+        }
+        return;
+      }
+    }
+    while (count <= 56) {
+      uint64_t b = 0;
       if (!hit_marker && pos < size) {
         b = data[pos];
         if (b == 0xff) {
@@ -90,7 +108,7 @@ struct Bits {
           pos++;
         }
       }
-      acc |= b << (24 - count);
+      acc |= b << (56 - count);
       count += 8;
     }
   }
@@ -101,7 +119,7 @@ struct Bits {
     if (count < n) {
       fill();
     }
-    const int v = static_cast<int>(acc >> (32 - n));
+    const int v = static_cast<int>(acc >> (64 - n));
     acc <<= n;
     count -= n;
     return v;
@@ -110,7 +128,7 @@ struct Bits {
     if (count < n) {
       fill();
     }
-    return static_cast<int>(acc >> (32 - n));
+    return static_cast<int>(acc >> (64 - n));
   }
   void skip(int n) {
     acc <<= n;
