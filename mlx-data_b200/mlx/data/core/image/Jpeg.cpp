@@ -22,6 +22,9 @@ struct Huffman {
   // codes of at most kLook bits, by their first kLook bits: length << 8 | value, 0 for longer codes
   static constexpr int kLook = 9;
   uint16_t look[1 << kLook];
+  // AC tables: when a code and the value bits after it fit in kLook bits, the
+  // decoded step at once: value << 8 | zero run << 4 | bits used; 0 otherwise
+  int16_t step[1 << kLook];
 
   // bits[l] = number of codes of length l (1..16), values in code order
   bool build(const unsigned char* bits, const unsigned char* vals, int count) {
@@ -46,6 +49,19 @@ struct Huffman {
         const int first = c << (kLook - l);
         for (int fill = 0; fill < (1 << (kLook - l)); fill++) {
           look[first + fill] = static_cast<uint16_t>(l << 8 | values[valptr[l] + i]);
+        }
+      }
+    }
+    for (int i = 0; i < (1 << kLook); i++) {
+      step[i] = 0;
+      const int l = look[i] >> 8, rs = look[i] & 0xff, size = rs & 15;
+      if (l && size && l + size <= kLook) {
+        int v = (i >> (kLook - l - size)) & ((1 << size) - 1);
+        if (v < (1 << (size - 1))) {
+          v -= (1 << size) - 1;
+        }
+        if (v >= -128 && v <= 127) {
+          step[i] = static_cast<int16_t>(v * 256 + (rs >> 4) * 16 + l + size);
         }
       }
     }
@@ -493,8 +509,19 @@ struct Decoder {
     }
     c.pred += t ? extend(b.get(t), t) : 0;
     coef[0] = c.pred;
+    const Huffman& act = ac[c.ta];
     for (int k = 1; k < 64;) {
-      const int rs = decode_symbol(b, ac[c.ta]);
+      const int quick = act.step[b.peek(Huffman::kLook)];
+      if (quick) {
+        k += (quick >> 4) & 15;
+        if (k > 63) {
+          return fail("corrupt entropy-coded data");
+        }
+        coef[kZigzag[k++]] = quick >> 8;
+        b.skip(quick & 15);
+        continue;
+      }
+      const int rs = decode_symbol(b, act);
       if (rs < 0) {
         return fail("corrupt entropy-coded data");
       }
