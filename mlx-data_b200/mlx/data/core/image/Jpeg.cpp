@@ -778,9 +778,55 @@ struct Decoder {
   }
 };
 
-// One output row (full resolution, `width` samples) of a component whose plane
-// is subsampled by (eh, ev): triangle filter, the nearer sample weighted 3:1,
-// edges repeated; the rounding biases alternate between neighbouring outputs.
+// Loops the compiler can vectorise get an AVX2 clone beside the baseline one;
+// the dynamic loader picks at start-up.
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+#define MLXD_CLONES __attribute__((target_clones("avx2", "default")))
+#else
+#define MLXD_CLONES
+#endif
+
+// Horizontal 2:1 triangle filter of n samples into 2n outputs (n >= 3):
+// out[2x] = (3 in[x] + in[x-1] + 1) >> 2, out[2x+1] = (3 in[x] + in[x+1] + 2) >> 2, edges copied.
+MLXD_CLONES void h2v1_row(const unsigned char* __restrict in, int64_t n, unsigned char* __restrict out) {
+  out[0] = in[0];
+  out[1] = static_cast<unsigned char>((3 * in[0] + in[1] + 2) >> 2);
+  for (int64_t x = 1; x < n - 1; x++) {
+    out[2 * x] = static_cast<unsigned char>((3 * in[x] + in[x - 1] + 1) >> 2);
+    out[2 * x + 1] = static_cast<unsigned char>((3 * in[x] + in[x + 1] + 2) >> 2);
+  }
+  out[2 * n - 2] = static_cast<unsigned char>((3 * in[n - 1] + in[n - 2] + 1) >> 2);
+  out[2 * n - 1] = in[n - 1];
+}
+
+// Both directions at once: col[x] = 3 near[x] + far[x], then
+// out[2x] = (3 col[x] + col[x-1] + 8) >> 4, out[2x+1] = (3 col[x] + col[x+1] + 7) >> 4.
+MLXD_CLONES void h2v2_row(const unsigned char* __restrict near, const unsigned char* __restrict far, int64_t n,
+                          int* __restrict col, unsigned char* __restrict out) {
+  for (int64_t x = 0; x < n; x++) {
+    col[x] = 3 * near[x] + far[x];
+  }
+  out[0] = static_cast<unsigned char>((col[0] * 4 + 8) >> 4);
+  out[1] = static_cast<unsigned char>((col[0] * 3 + col[1] + 7) >> 4);
+  for (int64_t x = 1; x < n - 1; x++) {
+    out[2 * x] = static_cast<unsigned char>((col[x] * 3 + col[x - 1] + 8) >> 4);
+    out[2 * x + 1] = static_cast<unsigned char>((col[x] * 3 + col[x + 1] + 7) >> 4);
+  }
+  out[2 * n - 2] = static_cast<unsigned char>((col[n - 1] * 3 + col[n - 2] + 8) >> 4);
+  out[2 * n - 1] = static_cast<unsigned char>((col[n - 1] * 4 + 7) >> 4);
+}
+
+MLXD_CLONES void h1v2_row(const unsigned char* __restrict near, const unsigned char* __restrict far, int64_t n, int bias,
+                          unsigned char* __restrict out) {
+  for (int64_t x = 0; x < n; x++) {
+    out[x] = static_cast<unsigned char>((3 * near[x] + far[x] + bias) >> 2);
+  }
+}
+
+// One output row (full resolution, `width` samples, room for one more) of a
+// component whose plane is subsampled by (eh, ev): triangle filter, the nearer
+// sample weighted 3:1, edges repeated; the rounding biases alternate between
+// neighbouring outputs.
 void upsampled_row(const Component& c, int eh, int ev, int64_t y, int64_t width, std::vector<int>& tmp, unsigned char* dst) {
   const size_t pitch = static_cast<size_t>(c.blocks_w) * 8;
   const int64_t n = c.dw;
@@ -789,8 +835,7 @@ void upsampled_row(const Component& c, int eh, int ev, int64_t y, int64_t width,
     return;
   }
   // planes of one or two columns are doubled without a filter, as libjpeg does
-  const bool box = eh == 2 && n <= 2;
-  if (box) {
+  if (eh == 2 && n <= 2) {
     const unsigned char* in = c.plane.data() + static_cast<size_t>(ev == 2 ? y >> 1 : y) * pitch;
     for (int64_t x = 0; x < width; x++) {
       dst[x] = in[x >> 1];
@@ -798,17 +843,7 @@ void upsampled_row(const Component& c, int eh, int ev, int64_t y, int64_t width,
     return;
   }
   if (ev == 1) {
-    const unsigned char* in = c.plane.data() + static_cast<size_t>(y) * pitch;
-    for (int64_t x = 0; x < n; x++) {
-      const int cur = in[x];
-      const int64_t a = 2 * x, b = 2 * x + 1;
-      if (a < width) {
-        dst[a] = static_cast<unsigned char>(x == 0 ? cur : (3 * cur + in[x - 1] + 1) >> 2);
-      }
-      if (b < width) {
-        dst[b] = static_cast<unsigned char>(x == n - 1 ? cur : (3 * cur + in[x + 1] + 2) >> 2);
-      }
-    }
+    h2v1_row(c.plane.data() + static_cast<size_t>(y) * pitch, n, dst);   // 2n >= width outputs
     return;
   }
   // two output rows per input row: the upper one leans on the row above, the lower on the row below
@@ -819,25 +854,28 @@ void upsampled_row(const Component& c, int eh, int ev, int64_t y, int64_t width,
   const unsigned char* in0 = c.plane.data() + static_cast<size_t>(iy) * pitch;
   const unsigned char* in1 = c.plane.data() + static_cast<size_t>(ny) * pitch;
   if (eh == 1) {
-    const int bias = lower ? 2 : 1;
-    for (int64_t x = 0; x < width; x++) {
-      dst[x] = static_cast<unsigned char>((3 * in0[x] + in1[x] + bias) >> 2);
-    }
+    h1v2_row(in0, in1, width, lower ? 2 : 1, dst);
     return;
   }
   tmp.resize(static_cast<size_t>(n));
-  for (int64_t x = 0; x < n; x++) {
-    tmp[x] = 3 * in0[x] + in1[x];
-  }
-  for (int64_t x = 0; x < n; x++) {
-    const int cur = tmp[x];
-    const int64_t a = 2 * x, b = 2 * x + 1;
-    if (a < width) {
-      dst[a] = static_cast<unsigned char>(x == 0 ? (cur * 4 + 8) >> 4 : (cur * 3 + tmp[x - 1] + 8) >> 4);
-    }
-    if (b < width) {
-      dst[b] = static_cast<unsigned char>(x == n - 1 ? (cur * 4 + 7) >> 4 : (cur * 3 + tmp[x + 1] + 7) >> 4);
-    }
+  h2v2_row(in0, in1, n, tmp.data(), dst);
+}
+
+// YCbCr -> RGB with 16 fractional bits (1.40200, 0.34414, 0.71414, 1.77200),
+// the products rounded as libjpeg's tables are.
+MLXD_CLONES void ycc_row(const unsigned char* __restrict yy, const unsigned char* __restrict cb,
+                         const unsigned char* __restrict cr, int64_t w, unsigned char* __restrict o) {
+  for (int64_t x = 0; x < w; x++) {
+    const int y0 = yy[x], u = cb[x] - 128, v = cr[x] - 128;
+    int rr = y0 + ((91881 * v + 32768) >> 16);
+    int gg = y0 + ((-22554 * u + 32768 - 46802 * v) >> 16);
+    int bb = y0 + ((116130 * u + 32768) >> 16);
+    rr = rr < 0 ? 0 : (rr > 255 ? 255 : rr);
+    gg = gg < 0 ? 0 : (gg > 255 ? 255 : gg);
+    bb = bb < 0 ? 0 : (bb > 255 ? 255 : bb);
+    o[3 * x] = static_cast<unsigned char>(rr);
+    o[3 * x + 1] = static_cast<unsigned char>(gg);
+    o[3 * x + 2] = static_cast<unsigned char>(bb);
   }
 }
 
@@ -886,22 +924,13 @@ bool jpeg_decode(const unsigned char* data, size_t size, unsigned char* out, std
     }
     return true;
   }
-  // YCbCr -> RGB with 16 fractional bits
-  int cr_r[256], cb_b[256], cr_g[256], cb_g[256];
-  for (int i = 0; i < 256; i++) {
-    const int x = i - 128;
-    cr_r[i] = (91881 * x + 32768) >> 16;     // 1.40200
-    cb_b[i] = (116130 * x + 32768) >> 16;    // 1.77200
-    cr_g[i] = -46802 * x;                    // 0.71414
-    cb_g[i] = -22554 * x + 32768;            // 0.34414
-  }
   // four components: the reference keeps the first three of libjpeg's CMYK output
   const bool rgb = d.is_rgb() || (d.ncomp == 4 && !d.is_ycck());
   const bool invert = d.is_ycck();
   std::vector<unsigned char> rows[3];
   std::vector<int> tmp;
   for (int i = 0; i < 3; i++) {
-    rows[i].resize(static_cast<size_t>(w));
+    rows[i].resize(static_cast<size_t>(w) + 2);   // a doubled row may be one sample longer than the image
   }
   for (int64_t y = 0; y < h; y++) {
     for (int i = 0; i < 3; i++) {
@@ -917,12 +946,7 @@ bool jpeg_decode(const unsigned char* data, size_t size, unsigned char* out, std
         o[3 * x + 2] = rows[2][x];
       }
     } else {
-      for (int64_t x = 0; x < w; x++) {
-        const int yy = rows[0][x], cb = rows[1][x], cr = rows[2][x];
-        o[3 * x] = clamp8(yy + cr_r[cr]);
-        o[3 * x + 1] = clamp8(yy + ((cb_g[cb] + cr_g[cr]) >> 16));
-        o[3 * x + 2] = clamp8(yy + cb_b[cb]);
-      }
+      ycc_row(rows[0].data(), rows[1].data(), rows[2].data(), w, o);
       if (invert) {
         for (int64_t x = 0; x < 3 * w; x++) {
           o[x] = static_cast<unsigned char>(255 - o[x]);
