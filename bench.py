@@ -180,7 +180,7 @@ def jpeg_fed_rate(dx, shapes, ops, batch, cast, lanes):
     dt = time.perf_counter() - t0
     return {"value": n_img / dt, "unit": "images/s", "decode_threads": threads, "images": n_img,
             "mean_file_bytes": int(np.mean([f.size for f in files])),
-            "decoder": "this package's (scalar, pixel-equal to libjpeg-turbo's defaults)"}
+            "decoder": "this package's (pixel-equal to libjpeg-turbo's defaults)"}
 
 
 def pool_shapes(wl, name, count):
